@@ -1,0 +1,309 @@
+// Uhat = row-normalised upper Cholesky factor of H^-1, computed without ever
+// forming H^-1:
+//
+//   H = T T^T with T upper triangular (a Cholesky factorisation that starts at the
+//   bottom-right corner), so chol_upper(H^-1) = T^-1 and, after dividing each row
+//   by its diagonal,  Uhat = diag(T) T^-1 = (T diag(T)^-1)^-1.
+//
+// One factorisation (C^3/3 flop) and one unit-triangular inverse (C^3/3) replace
+// the reference's potrf + potri + potrf (src/linalg_utils.py:12,
+// src/gptq.py:237-242; about 4C^3/3 flop).
+//
+// Blocked right-looking factorisation with 128-wide panels processed from the last
+// panel to the first:
+//   1. chol_diag_rev_kernel  : the 128x128 diagonal block, one CTA, register tiled;
+//   2. trsm_rows_kernel      : the panel above it, one warp per row, substitution
+//                              against the diagonal block staged in shared memory;
+//   3. a GEMM (GemmDesc)     : trailing update of the upper triangle.
+// The inverse is built by inverting the 128x128 diagonal blocks (same substitution
+// kernel on identity rows) and then merging neighbouring blocks pairwise,
+//   inv([A B; 0 D]) = [A^-1, -A^-1 B D^-1; 0, D^-1],
+// log2(C/128) levels of two batched GEMMs each.
+#include "gemm.cuh"
+#include "engine.cuh"
+
+namespace mq {
+
+namespace {
+
+constexpr int NB = 128;  // panel width
+
+// ------------------------------------------------------------------ diagonal block
+// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads, thread
+// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers.
+__global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
+                                                            int k_global, mq_layer_flags* flags) {
+  __shared__ float colv[NB];
+  __shared__ float piv;
+  const int t = threadIdx.x;
+  const int tr = t >> 4, tc = t & 15;
+  float a[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int r = tr * 8 + i, c = tc * 8 + j;
+      a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
+    }
+  for (int kt = 15; kt >= 0; --kt) {
+#pragma unroll
+    for (int kk = 7; kk >= 0; --kk) {
+      const int k = kt * 8 + kk;
+      if (tr == kt && tc == kt) piv = a[kk][kk];
+      __syncthreads();
+      float d = piv;
+      if (!(d > 0.0f)) {  // also catches NaN
+        if (t == 0 && k < nb) atomicCAS(&flags->not_positive, 0, k_global + k + 1);
+        d = 1.0f;
+      }
+      const float tkk = sqrtf(d);
+      if (tc == kt && tr <= kt) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int row = tr * 8 + i;
+          if (row < k) {
+            a[i][kk] = a[i][kk] / tkk;
+            colv[row] = a[i][kk];
+          }
+        }
+        if (tr == kt) a[kk][kk] = tkk;
+      }
+      __syncthreads();
+      if (tr <= tc && tc <= kt) {
+        float ci[8], cj[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ci[i] = colv[tr * 8 + i];
+          cj[i] = colv[tc * 8 + i];
+        }
+        if (tc < kt) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-ci[i], cj[j], a[i][j]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j < kk) a[i][j] = fmaf(-ci[i], cj[j], a[i][j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int r = tr * 8 + i, c = tc * 8 + j;
+      if (r < nb && c < nb) blk[(int64_t)r * ld + c] = (r <= c) ? a[i][j] : 0.0f;
+    }
+}
+
+// ------------------------------------------------------------------ substitution
+// Solves P T^T = A row by row, T the (nb x nb) upper-triangular block at `tblk`:
+//   for k = nb-1 .. 0:  p_k = a_k / T[k,k];  a_j -= p_k T[j,k]  (j < k).
+// One warp per row; lane l holds columns 4l..4l+3.  T is staged transposed in shared
+// memory so that a lane reads the four T[j,k] it needs as one float4.
+// IDENTITY: the right-hand side is I and the result is stored transposed, which
+// yields T^-1 (upper triangular) in `rows`.
+constexpr int TT_LD = NB + 4;
+
+template <bool IDENTITY>
+__global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict__ tblk, int64_t ldt, int64_t t_bs,
+                                                        float* __restrict__ rows, int64_t ldr, int64_t r_bs,
+                                                        int nrows, int nb_full, int n_total) {
+  extern __shared__ __align__(16) float smem[];
+  float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
+  float* dg = smem + NB * TT_LD;   // [NB]
+  const int b = blockIdx.y;
+  int nb = nb_full;
+  if (n_total > 0) {  // batched over diagonal blocks: the last one may be narrower
+    int left = n_total - b * nb_full;
+    nb = left < nb_full ? left : nb_full;
+    if (IDENTITY) nrows = nb;
+  }
+  tblk += (int64_t)b * t_bs;
+  rows += (int64_t)b * r_bs;
+  for (int idx = threadIdx.x; idx < NB * NB; idx += blockDim.x) {
+    int j = idx >> 7, k = idx & 127;  // element T[j][k], coalesced over k
+    float v = (j < nb && k < nb) ? tblk[(int64_t)j * ldt + k] : (j == k ? 1.0f : 0.0f);
+    TT[k * TT_LD + j] = (j < k) ? v : 0.0f;
+    if (j == k) dg[k] = v;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < nrows; r += gridDim.x * warps_per_block) {
+    float a[4];
+    float* rp = rows + (int64_t)r * ldr;
+    if (IDENTITY) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) a[q] = (lane * 4 + q == r) ? 1.0f : 0.0f;
+    } else if (lane * 4 < nb) {
+      float4 v = *reinterpret_cast<const float4*>(rp + lane * 4);
+      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+    } else {
+      a[0] = a[1] = a[2] = a[3] = 0.0f;
+    }
+    for (int kq = (nb >> 2) - 1; kq >= 0; --kq) {
+#pragma unroll
+      for (int kk = 3; kk >= 0; --kk) {
+        const int k = kq * 4 + kk;
+        float p = a[kk] / dg[k];
+        p = __shfl_sync(0xffffffffu, p, kq);
+        const float4 tt = *reinterpret_cast<const float4*>(&TT[k * TT_LD + lane * 4]);
+        a[0] = fmaf(-p, tt.x, a[0]);
+        a[1] = fmaf(-p, tt.y, a[1]);
+        a[2] = fmaf(-p, tt.z, a[2]);
+        a[3] = fmaf(-p, tt.w, a[3]);
+        if (lane == kq) a[kk] = p;
+      }
+    }
+    if (lane * 4 < nb) {
+      if (IDENTITY) {
+        // result row r is column r of T^-1
+#pragma unroll
+        for (int q = 0; q < 4; ++q) rows[(int64_t)(lane * 4 + q) * ldr + r] = a[q];
+      } else {
+        *reinterpret_cast<float4*>(rp + lane * 4) = make_float4(a[0], a[1], a[2], a[3]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ small passes
+__global__ void __launch_bounds__(256) extract_diag_kernel(const float* __restrict__ H, int64_t C, int64_t ld,
+                                                           float* __restrict__ diag) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < C) diag[i] = H[i * ld + i];
+}
+
+// T -> T diag(T)^-1 on the upper triangle (unit diagonal), zeros below it.
+__global__ void __launch_bounds__(256) scale_columns_kernel(float* __restrict__ H, int64_t C, int64_t ld,
+                                                            const float* __restrict__ diag) {
+  int64_t r = blockIdx.y;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < C; c += (int64_t)gridDim.x * blockDim.x) {
+    float v = H[r * ld + c];
+    H[r * ld + c] = (c > r) ? v / diag[c] : (c == r ? 1.0f : 0.0f);
+  }
+}
+
+__global__ void __launch_bounds__(256) identity_if_failed_kernel(float* __restrict__ U, int64_t C, int64_t ld,
+                                                                 const mq_layer_flags* flags) {
+  if (flags->not_positive == 0) return;
+  int64_t n = C * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / C, c = i - r * C;
+    U[r * ld + c] = (r == c) ? 1.0f : 0.0f;
+  }
+}
+
+constexpr size_t kTrsmSmem = (size_t)(NB * TT_LD + NB) * sizeof(float);
+
+int configure_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  MQ_CUDA(cudaGetDevice(&dev));
+  if (!done[dev & 63]) {
+    MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
+    MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
+    done[dev & 63] = true;
+  }
+  return MQ_OK;
+}
+
+}  // namespace
+
+size_t hinv_workspace_bytes(int64_t C, int math, int split) {
+  size_t bytes = align_up((size_t)C * sizeof(float), 256);          // diag
+  bytes += align_up((size_t)C * (size_t)C * sizeof(float), 256);    // merge scratch
+  bytes += engine_workspace_bytes(C, C, C, math, split);
+  return bytes;
+}
+
+int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float* diag_out, int math, int split,
+               mq_layer_flags* flags, Workspace& ws, cudaStream_t st) {
+  MQ_TRY(configure_once());
+  float* diag = ws.take<float>(C);
+  float* scratch = ws.take<float>((size_t)C * C);
+  MQ_REQUIRE(diag && scratch, MQ_ERR_WORKSPACE, "mq_hinv_upper: workspace too small");
+  Engine eng(math, split, ws, st);
+
+  const int P = (int)ceil_div(C, NB);
+  // ---- factorisation, last panel first
+  for (int p = P - 1; p >= 0; --p) {
+    const int64_t k1 = (int64_t)p * NB;
+    const int nb = (int)((C - k1) < NB ? (C - k1) : NB);
+    float* dblk = H + k1 * ldh + k1;
+    chol_diag_rev_kernel<<<1, 256, 0, st>>>(dblk, ldh, nb, (int)k1, flags);
+    MQ_LAUNCH_CHECK();
+    if (k1 == 0) break;
+    int grid = (int)(ceil_div(k1, 8) < 148 * 2 ? ceil_div(k1, 8) : 148 * 2);
+    trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0);
+    MQ_LAUNCH_CHECK();
+    GemmDesc g;
+    g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;
+    g.B = H + k1; g.b_rs = 1; g.b_cs = ldh;
+    g.C = H; g.ldc = ldh;
+    g.M = (int)k1; g.N = (int)k1; g.K = nb;
+    g.alpha = -1.0f; g.beta = 1.0f;
+    g.upper_tiles_only = 1;
+    MQ_TRY(eng.gemm(g));
+  }
+  // ---- T -> unit-diagonal factor, then its inverse
+  extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
+  MQ_LAUNCH_CHECK();
+  if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag);
+  MQ_LAUNCH_CHECK();
+  MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
+  trsm_rows_kernel<true><<<dim3(16, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
+                                                             (int64_t)NB * (ldu + 1), NB, NB, (int)C);
+  MQ_LAUNCH_CHECK();
+  for (int64_t s = NB; s < C; s *= 2) {
+    const int batch = (int)ceil_div(C - s, 2 * s);
+    GemmDesc g1;  // scratch block = B D^-1
+    g1.A = H + s; g1.a_rs = ldh; g1.a_cs = 1; g1.a_bs = 2 * s * (ldh + 1);
+    g1.B = Uhat + s * ldu + s; g1.b_rs = ldu; g1.b_cs = 1; g1.b_bs = 2 * s * (ldu + 1);
+    g1.C = scratch + s; g1.ldc = C; g1.c_bs = 2 * s * (C + 1);
+    g1.M = (int)s; g1.N = (int)s; g1.K = (int)s;
+    g1.alpha = 1.0f; g1.beta = 0.0f;
+    g1.b_upper = 1;
+    g1.batch = batch; g1.n_total = (int)(C - s); g1.n_step = (int)(2 * s); g1.k_follows_n = 1;
+    MQ_TRY(eng.gemm(g1));
+    GemmDesc g2;  // off-diagonal block = -A^-1 (scratch block)
+    g2.A = Uhat; g2.a_rs = ldu; g2.a_cs = 1; g2.a_bs = 2 * s * (ldu + 1);
+    g2.B = scratch + s; g2.b_rs = C; g2.b_cs = 1; g2.b_bs = 2 * s * (C + 1);
+    g2.C = Uhat + s; g2.ldc = ldu; g2.c_bs = 2 * s * (ldu + 1);
+    g2.M = (int)s; g2.N = (int)s; g2.K = (int)s;
+    g2.alpha = -1.0f; g2.beta = 0.0f;
+    g2.a_upper = 1;
+    g2.batch = batch; g2.n_total = (int)(C - s); g2.n_step = (int)(2 * s);
+    MQ_TRY(eng.gemm(g2));
+  }
+  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(Uhat, C, ldu, flags);
+  MQ_LAUNCH_CHECK();
+  return MQ_OK;
+}
+
+}  // namespace mq
+
+extern "C" size_t mq_hinv_upper_workspace_bytes(int64_t C, int math, int split) {
+  if (C <= 0) return 0;
+  return mq::hinv_workspace_bytes(C, math, split);
+}
+
+extern "C" int mq_hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float* diag_out, int math, int split,
+                             mq_layer_flags* flags, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(H && Uhat && flags, MQ_ERR_ARGUMENT, "mq_hinv_upper: null pointer");
+  MQ_REQUIRE(C > 0 && ldh >= C && ldu >= C, MQ_ERR_ARGUMENT, "mq_hinv_upper: bad C=%lld ldh=%lld ldu=%lld", (long long)C,
+             (long long)ldh, (long long)ldu);
+  MQ_REQUIRE(C % 8 == 0, MQ_ERR_UNSUPPORTED, "mq_hinv_upper: C=%lld must be a multiple of 8", (long long)C);
+  MQ_REQUIRE(ldh % 4 == 0 && ldu % 4 == 0 && aligned(H, 16) && aligned(Uhat, 16), MQ_ERR_ALIGNMENT,
+             "mq_hinv_upper: H and Uhat must be 16-byte aligned with leading dimensions that are multiples of 4");
+  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_hinv_upper: bad math %d", math);
+  Workspace ws(workspace, workspace_bytes);
+  return hinv_upper(H, C, ldh, Uhat, ldu, diag_out, math, split, flags, ws, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,188 @@
+// GPTQ column sweep.  Replaces the 2*C Triton launches and C/B cuBLAS calls of the
+// reference's captured loop (src/gptq_loop.py:141-148) with, per 128-column tile,
+// ONE sweep kernel plus ONE GEMM.
+//
+// Sweep kernel: a warp owns one weight row; lane l keeps columns 4l..4l+3 of the
+// current tile in registers.  Column j is quantized by the lane that owns it
+//   q = clamp(floor(x/s + z + 0.5), 0, maxq)   y = round_to_dtype((q - z) s)   e = y - x
+// (src/gptq_loop.py:28-40, src/quant_utils.py:30-49), e is broadcast with one
+// shuffle and every lane applies  w_k += Uhat[j,k] e  to its columns k > j with the
+// row Uhat[j, tile] read from shared memory (src/gptq_loop.py:83-88).  Rows are
+// independent, so there is no synchronisation after the tile of Uhat is staged.
+//
+// The errors of the tile (R x 128) go to a scratch matrix and the lazy update
+//   W[:, later] += E Uhat[tile, later]             (src/gptq_loop.py:148)
+// is a GEMM through the Engine.  Codes are written straight into the (R, C) uint8
+// result, so the transposes of src/gptq.py:191-199 never happen.
+#include "engine.cuh"
+
+namespace mq {
+
+namespace {
+
+constexpr int TILE = 128;
+constexpr int SWEEP_THREADS = 512;  // 16 rows per CTA
+
+template <int DT>
+__global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
+    const float* __restrict__ W, int64_t ldw, int R, const float* __restrict__ U, int64_t ldu,
+    const float* __restrict__ scale, const float* __restrict__ zero, int64_t group, int64_t s_rs, int64_t s_gs,
+    float maxq, float zero_default, uint8_t* __restrict__ codes, int64_t C,
+    typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb) {
+  using T = typename StorageOf<DT>::type;
+  extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
+  for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
+    int j = idx >> 5, k4 = (idx & 31) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j < nb && k4 < nb && k4 + 3 > j) {
+      v = __ldg(reinterpret_cast<const float4*>(U + (int64_t)(i1 + j) * ldu + i1 + k4));
+      if (k4 + 0 <= j) v.x = 0.f;
+      if (k4 + 1 <= j) v.y = 0.f;
+      if (k4 + 2 <= j) v.z = 0.f;
+    }
+    *reinterpret_cast<float4*>(&ublk[j * TILE + k4]) = v;
+  }
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (SWEEP_THREADS / 32) + (threadIdx.x >> 5);
+  if (r >= R) return;
+  const int c0 = i1 + lane * 4;
+  const bool have = lane * 4 < nb;  // nb is a multiple of 4
+
+  float w[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {1.f, 1.f, 1.f, 1.f}, zr[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) zr[t] = zero_default;
+  if (have) {
+    float4 v = *reinterpret_cast<const float4*>(W + (int64_t)r * ldw + c0);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      int64_t off = (int64_t)r * s_rs + ((c0 + t) / group) * s_gs;
+      sc[t] = __ldg(scale + off);
+      if (zero) zr[t] = __ldg(zero + off);
+    }
+  }
+  float qv[4] = {0.f, 0.f, 0.f, 0.f}, yv[4] = {0.f, 0.f, 0.f, 0.f}, ev[4] = {0.f, 0.f, 0.f, 0.f};
+
+  const int n_quads = nb >> 2;
+  for (int jq = 0; jq < n_quads; ++jq) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      // Every lane evaluates the grid on its own element; only lane jq's value is used.
+      const float x = w[t];
+      const float q = fminf(fmaxf(floorf((x / sc[t] + zr[t]) + 0.5f), 0.0f), maxq);
+      const float y = round_through<DT>((q - zr[t]) * sc[t]);
+      const float e = y - x;
+      if (lane == jq) { qv[t] = q; yv[t] = y; ev[t] = e; }
+      const float eb = __shfl_sync(0xffffffffu, e, jq);
+      const float4 u = *reinterpret_cast<const float4*>(&ublk[(jq * 4 + t) * TILE + lane * 4]);
+      w[0] = fmaf(u.x, eb, w[0]);
+      w[1] = fmaf(u.y, eb, w[1]);
+      w[2] = fmaf(u.z, eb, w[2]);
+      w[3] = fmaf(u.w, eb, w[3]);
+    }
+  }
+  if (have) {
+    uchar4 qc = make_uchar4((unsigned char)qv[0], (unsigned char)qv[1], (unsigned char)qv[2], (unsigned char)qv[3]);
+    *reinterpret_cast<uchar4*>(codes + (int64_t)r * C + c0) = qc;
+    if (deq) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) deq[(int64_t)r * C + c0 + t] = from_float<T>(yv[t]);
+    }
+  }
+  // columns past nb of a narrow last tile hold zeros so the GEMM may read all 128
+  *reinterpret_cast<float4*>(err + (int64_t)r * TILE + lane * 4) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+}
+
+int configure_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  MQ_CUDA(cudaGetDevice(&dev));
+  if (!done[dev & 63]) {
+    const int bytes = TILE * TILE * (int)sizeof(float);
+    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[dev & 63] = true;
+  }
+  return MQ_OK;
+}
+
+}  // namespace
+
+size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
+  return align_up((size_t)R * TILE * sizeof(float), 256) + engine_workspace_bytes(R, C, TILE, math, split);
+}
+
+int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
+               const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
+               void* deq, int math, int split, Workspace& ws, cudaStream_t st) {
+  MQ_TRY(configure_once());
+  float* err = ws.take<float>((size_t)R * TILE);
+  MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
+  Engine eng(math, split, ws, st);
+  const float maxq = (float)((1 << bits) - 1);
+  const float zero_default = 0.5f * (float)(1 << bits);
+  const int grid = (int)ceil_div(R, SWEEP_THREADS / 32);
+  const size_t smem = TILE * TILE * sizeof(float);
+  for (int64_t i1 = 0; i1 < C; i1 += TILE) {
+    const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
+    switch (out_dtype) {
+      case MQ_F32:
+        sweep_tile_kernel<MQ_F32><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+                                                                  maxq, zero_default, codes, C, static_cast<float*>(deq), err,
+                                                                  (int)i1, nb);
+        break;
+      case MQ_BF16:
+        sweep_tile_kernel<MQ_BF16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+                                                                   maxq, zero_default, codes, C,
+                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb);
+        break;
+      default:
+        sweep_tile_kernel<MQ_F16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+                                                                  maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
+                                                                  (int)i1, nb);
+    }
+    MQ_LAUNCH_CHECK();
+    const int64_t i2 = i1 + nb;
+    if (i2 < C) {
+      GemmDesc g;
+      g.A = err; g.a_rs = TILE; g.a_cs = 1;
+      g.B = Uhat + i1 * ldu + i2; g.b_rs = ldu; g.b_cs = 1;
+      g.C = W + i2; g.ldc = ldw;
+      g.M = (int)R; g.N = (int)(C - i2); g.K = nb;
+      g.alpha = 1.0f; g.beta = 1.0f;
+      MQ_TRY(eng.gemm(g));
+    }
+  }
+  return MQ_OK;
+}
+
+}  // namespace mq
+
+extern "C" size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
+  if (R <= 0 || C <= 0) return 0;
+  return mq::sweep_workspace_bytes(R, C, math, split);
+}
+
+extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu,
+                             const float* scale, const float* zero, int64_t group, int64_t row_stride,
+                             int64_t group_stride, int bits, int out_dtype, uint8_t* codes, void* dequantized, int math,
+                             int split, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(W && Uhat && scale && codes, MQ_ERR_ARGUMENT, "mq_gptq_sweep: null pointer");
+  MQ_REQUIRE(R > 0 && C > 0 && ldw >= C && ldu >= C, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad shape R=%lld C=%lld ldw=%lld ldu=%lld",
+             (long long)R, (long long)C, (long long)ldw, (long long)ldu);
+  MQ_REQUIRE(group > 0 && C % group == 0, MQ_ERR_ARGUMENT, "mq_gptq_sweep: group %lld does not divide C=%lld", (long long)group,
+             (long long)C);
+  MQ_REQUIRE(bits >= 2 && bits <= 8, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bits=%d", bits);
+  MQ_REQUIRE(valid_dtype(out_dtype), MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad dtype %d", out_dtype);
+  MQ_REQUIRE(C % 8 == 0, MQ_ERR_UNSUPPORTED, "mq_gptq_sweep: C=%lld must be a multiple of 8", (long long)C);
+  MQ_REQUIRE(ldw % 4 == 0 && ldu % 4 == 0 && aligned(W, 16) && aligned(Uhat, 16) && aligned(codes, 4), MQ_ERR_ALIGNMENT,
+             "mq_gptq_sweep: W/Uhat need 16-byte alignment and leading dimensions that are multiples of 4");
+  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad math %d", math);
+  Workspace ws(workspace, workspace_bytes);
+  return gptq_sweep(W, R, C, ldw, Uhat, ldu, scale, zero, group, row_stride, group_stride, bits, out_dtype, codes,
+                    dequantized, math, split, ws, static_cast<cudaStream_t>(stream));
+}

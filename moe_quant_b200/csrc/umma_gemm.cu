@@ -1,0 +1,528 @@
+// tcgen05 tensor-core GEMM on bf16/fp16 planes: the MQ_MATH_TENSOR arithmetic.
+//
+//   C[m,n] = alpha * sum over terms (i,j) of  A_i[m,:] . B_j[n,:]  + beta * C[m,n]
+//
+// A_i / B_j are 16-bit "planes" of the operands, both stored K-major (the reduction
+// index contiguous) so that a 128 x 64 tile is 128 rows of 128 bytes: exactly one TMA
+// box with the 128-byte swizzle and exactly the canonical K-major shared-memory
+// layout that tcgen05.mma reads through a matrix descriptor.  An fp32 operand x is cut
+// into planes hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid); products of two
+// bf16 numbers are exact in fp32, so keeping the terms with i + j < planes recovers
+// fp32-grade products (planes = 3: six products, error ~2^-24) on the tensor pipe.
+//
+// Kernel structure (one 128 x 128 output tile per CTA, 192 threads):
+//   warp 0, one lane : TMA producer, fills a ring of shared-memory stages
+//   warp 1, one lane : issues tcgen05.mma (M128 N128 K16) into a 128-column TMEM
+//                      accumulator, releases stages with tcgen05.commit
+//   warps 2..5       : epilogue, tcgen05.ld the accumulator (one TMEM lane = one output
+//                      row per thread), alpha/beta, bounds, stores
+// Every mbarrier wait is bounded; a wait that expires records a code in g_engine_fault,
+// the kernel still frees its TMEM and returns.
+#include <cuda.h>
+
+#include "engine.cuh"
+
+namespace mq {
+
+__device__ int g_engine_fault = 0;
+
+namespace {
+
+constexpr int TILE_M = 128, TILE_N = 128, SLAB_K = 64;
+constexpr int PLANE_TILE_BYTES = TILE_M * SLAB_K * 2;  // 16 KB
+constexpr int GEMM_THREADS = 192;
+constexpr int MAX_TERMS = 6;
+
+struct UmmaParams {
+  float* C;
+  int64_t ldc, c_bs;
+  int M, N, K;
+  float alpha, beta;
+  int upper_tiles_only, a_upper, b_upper;
+  int n_total, n_step, k_follows_n;
+  int a_rows_pad, b_rows_pad;  // rows each batch occupies in the stacked plane buffers
+  int planes, nterms, stages;
+  unsigned char term_a[MAX_TERMS], term_b[MAX_TERMS];
+  uint32_t idesc;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: gives up after about two seconds and records `code`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) {
+        atomicCAS(&g_engine_fault, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset: unused with a swizzle
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // version
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+
+// ---------------------------------------------------------------- the GEMM kernel
+__global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                 const __grid_constant__ CUtensorMap map_b,
+                                                                 const UmmaParams p) {
+  const int b = blockIdx.z;
+  const int m0 = blockIdx.y * TILE_M, n0 = blockIdx.x * TILE_N;
+  int N = p.N, K = p.K;
+  if (p.n_step) {
+    int left = p.n_total - b * p.n_step;
+    N = N < left ? N : left;
+    if (p.k_follows_n) K = N;
+  }
+  if (N <= 0 || n0 >= N || m0 >= p.M) return;
+  if (p.upper_tiles_only && n0 + TILE_N <= m0) return;
+  const int k_lo = p.a_upper ? (m0 / SLAB_K) * SLAB_K : 0;
+  int k_hi = K;
+  if (p.b_upper && n0 + TILE_N < k_hi) k_hi = n0 + TILE_N;
+  const int n_slabs = k_hi > k_lo ? (k_hi - k_lo + SLAB_K - 1) / SLAB_K : 0;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
+  const uint32_t stage_bytes = (uint32_t)p.planes * 2u * PLANE_TILE_BYTES;
+  __shared__ __align__(8) uint64_t bars[2 * 4 + 1];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]), acc_bar = smem_u32(&bars[8]);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TILE_N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int a_row = b * p.a_rows_pad + m0, b_row = b * p.b_rows_pad + n0;
+      for (int s = 0; s < n_slabs; ++s) {
+        const int st = s % p.stages;
+        if (s >= p.stages && !mbar_wait(empty0 + 8 * st, ((s / p.stages) - 1) & 1, 1)) break;
+        mbar_expect_tx(full0 + 8 * st, stage_bytes);
+        const uint32_t dst = smem_base + st * stage_bytes;
+        const int k = k_lo + s * SLAB_K;
+        for (int pl = 0; pl < p.planes; ++pl) {
+          tma_load_3d(dst + pl * PLANE_TILE_BYTES, &map_a, full0 + 8 * st, k, a_row, pl);
+          tma_load_3d(dst + (p.planes + pl) * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, k, b_row, pl);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t accumulate = 0;
+      bool ok = true;
+      for (int s = 0; s < n_slabs && ok; ++s) {
+        const int st = s % p.stages;
+        ok = mbar_wait(full0 + 8 * st, (s / p.stages) & 1, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_base + st * stage_bytes;
+        const uint32_t b_base = a_base + p.planes * PLANE_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < SLAB_K / 16; ++kk) {
+          for (int t = 0; t < p.nterms; ++t) {
+            const uint64_t ad = kmajor_sw128_desc(a_base + p.term_a[t] * PLANE_TILE_BYTES + kk * 32);
+            const uint64_t bd = kmajor_sw128_desc(b_base + p.term_b[t] * PLANE_TILE_BYTES + kk * 32);
+            umma_bf16(tmem_acc, ad, bd, p.idesc, accumulate);
+            accumulate = 1;
+          }
+        }
+        umma_commit(empty0 + 8 * st);  // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_bar);  // arrives when every MMA issued above has completed
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const bool have_acc = n_slabs > 0;
+    bool ok = true;
+    if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
+    tc_fence_after();
+    float* __restrict__ C = p.C + (int64_t)b * p.c_bs;
+    const int row = m0 + q * 32 + lane;
+    const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < TILE_N / 32; ++c) {
+        float v[32];
+        if (have_acc) {
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        }
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < N) {
+          float* dst = C + (int64_t)row * p.ldc + col0;
+          if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
+              if (p.beta != 0.0f) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
+                o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < N) {
+                float o = p.alpha * v[j];
+                if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
+                dst[j] = o;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, TILE_N);
+  }
+}
+
+// ---------------------------------------------------------------- operand planes
+// dst plane pl, batch b, row r, k  <-  piece pl of src[b][r][k]; zero outside the logical
+// (rows_b x K_b) extent up to the padded (rows_pad x K_pad) one.  32 x 32 tiles; when the
+// source is contiguous along its row index the tile is transposed through shared memory
+// so that both the global read and the global write are coalesced.
+struct SplitParams {
+  const void* src;
+  int64_t rs, cs, bs;  // element strides of the source: row, k, batch
+  int rows, K;         // logical extent per batch
+  int rows_pad, K_pad;
+  int planes;
+  uint16_t* dst;
+  int64_t plane_stride;
+  // ragged last batch (see GemmDesc): rows_b = min(rows, row_total - b*row_step) etc.
+  int row_total, row_step, k_total, k_step;
+};
+
+template <typename T>
+__device__ __forceinline__ void split_store(float x, int planes, uint16_t* dst, int64_t idx, int64_t plane_stride);
+
+template <>
+__device__ __forceinline__ void split_store<__nv_bfloat16>(float x, int planes, uint16_t* dst, int64_t idx, int64_t ps) {
+  __nv_bfloat16 h = __float2bfloat16_rn(x);
+  dst[idx] = __bfloat16_as_ushort(h);
+  if (planes > 1) {
+    float r1 = x - __bfloat162float(h);
+    __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    dst[idx + ps] = __bfloat16_as_ushort(m);
+    if (planes > 2) {
+      float r2 = r1 - __bfloat162float(m);
+      dst[idx + 2 * ps] = __bfloat16_as_ushort(__float2bfloat16_rn(r2));
+    }
+  }
+}
+template <>
+__device__ __forceinline__ void split_store<__half>(float x, int, uint16_t* dst, int64_t idx, int64_t) {
+  dst[idx] = __half_as_ushort(__float2half_rn(x));  // fp16 activations enter as one exact plane
+}
+
+template <typename TIn, typename TPlane, bool TRANSPOSE>
+__global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  int rows = p.rows, K = p.K;
+  if (p.row_step) { int left = p.row_total - b * p.row_step; rows = rows < left ? rows : left; }
+  if (p.k_step) { int left = p.k_total - b * p.k_step; K = K < left ? K : left; }
+  const TIn* __restrict__ src = static_cast<const TIn*>(p.src) + (int64_t)b * p.bs;
+  const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  if (TRANSPOSE) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int r = r0 + tx, k = k0 + ty + 8 * i;
+      tile[ty + 8 * i][tx] = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rl = ty + 8 * i;
+    const int r = r0 + rl, k = k0 + tx;
+    if (r >= p.rows_pad || k >= p.K_pad) continue;
+    float x;
+    if (TRANSPOSE) x = tile[tx][rl];
+    else x = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+    split_store<TPlane>(x, p.planes, p.dst, ((int64_t)b * p.rows_pad + r) * p.K_pad + k, p.plane_stride);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encoder(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    MQ_REQUIRE(sym && qres == cudaDriverEntryPointSuccess, MQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  *out = fn;
+  return MQ_OK;
+}
+
+// Planes of one operand: [planes][total_rows][K_pad] 16-bit elements.
+struct PlaneSet {
+  uint16_t* base = nullptr;
+  int planes = 0;
+  int64_t total_rows = 0;  // batch * rows_pad
+  int rows_pad = 0;
+  int K_pad = 0;
+  bool fp16 = false;
+};
+
+int encode_map(const PlaneSet& ps, CUtensorMap* map) {
+  EncodeTiledFn enc;
+  MQ_TRY(get_encoder(&enc));
+  cuuint64_t dims[3] = {(cuuint64_t)ps.K_pad, (cuuint64_t)ps.total_rows, (cuuint64_t)ps.planes};
+  cuuint64_t strides[2] = {(cuuint64_t)ps.K_pad * 2, (cuuint64_t)ps.K_pad * 2 * (cuuint64_t)ps.total_rows};
+  cuuint32_t box[3] = {SLAB_K, TILE_M, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, ps.fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ps.base, dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MQ_REQUIRE(r == CUDA_SUCCESS, MQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (K_pad=%d rows=%lld planes=%d)", (int)r,
+             ps.K_pad, (long long)ps.total_rows, ps.planes);
+  return MQ_OK;
+}
+
+int pad_to(int x, int a) { return (x + a - 1) / a * a; }
+
+template <typename TIn, typename TPlane>
+int launch_split(const SplitParams& sp, int batch, cudaStream_t st) {
+  dim3 grid((unsigned)(sp.K_pad / 32), (unsigned)(sp.rows_pad / 32), (unsigned)batch);
+  if (sp.rs == 1 && sp.cs != 1)
+    split_planes_kernel<TIn, TPlane, true><<<grid, 256, 0, st>>>(sp);
+  else
+    split_planes_kernel<TIn, TPlane, false><<<grid, 256, 0, st>>>(sp);
+  MQ_LAUNCH_CHECK();
+  return MQ_OK;
+}
+
+int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t bs, int rows, int K, int batch, int planes,
+                int row_total, int row_step, int k_total, int k_step, Workspace& ws, PlaneSet* out, cudaStream_t st) {
+  PlaneSet ps;
+  ps.planes = in_dtype == MQ_F32 ? planes : 1;
+  ps.rows_pad = pad_to(rows, TILE_M);
+  ps.K_pad = pad_to(K, SLAB_K);
+  ps.total_rows = (int64_t)batch * ps.rows_pad;
+  ps.fp16 = in_dtype == MQ_F16;
+  const size_t elems = (size_t)ps.planes * ps.total_rows * ps.K_pad;
+  ps.base = ws.take<uint16_t>(elems);
+  MQ_REQUIRE(ps.base, MQ_ERR_WORKSPACE, "tensor engine: workspace too small for %zu plane elements", elems);
+  SplitParams sp;
+  sp.src = src; sp.rs = rs; sp.cs = cs; sp.bs = bs;
+  sp.rows = rows; sp.K = K; sp.rows_pad = ps.rows_pad; sp.K_pad = ps.K_pad;
+  sp.planes = ps.planes; sp.dst = ps.base; sp.plane_stride = ps.total_rows * ps.K_pad;
+  sp.row_total = row_total; sp.row_step = row_step; sp.k_total = k_total; sp.k_step = k_step;
+  switch (in_dtype) {
+    case MQ_F32: MQ_TRY((launch_split<float, __nv_bfloat16>(sp, batch, st))); break;
+    case MQ_BF16: MQ_TRY((launch_split<__nv_bfloat16, __nv_bfloat16>(sp, batch, st))); break;
+    default: MQ_TRY((launch_split<__half, __half>(sp, batch, st)));
+  }
+  *out = ps;
+  return MQ_OK;
+}
+
+int configure_once() {
+  static bool done[64] = {};
+  int dev = 0;
+  MQ_CUDA(cudaGetDevice(&dev));
+  if (!done[dev & 63]) {
+    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    done[dev & 63] = true;
+  }
+  return MQ_OK;
+}
+
+int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStream_t st) {
+  MQ_TRY(configure_once());
+  CUtensorMap map_a, map_b;
+  MQ_TRY(encode_map(A, &map_a));
+  MQ_TRY(encode_map(B, &map_b));
+  UmmaParams p;
+  p.C = d.C; p.ldc = d.ldc; p.c_bs = d.c_bs;
+  p.M = d.M; p.N = d.N; p.K = d.K;
+  p.alpha = d.alpha; p.beta = d.beta;
+  p.upper_tiles_only = d.upper_tiles_only; p.a_upper = d.a_upper; p.b_upper = d.b_upper;
+  p.n_total = d.n_total; p.n_step = d.n_step; p.k_follows_n = d.k_follows_n;
+  p.a_rows_pad = A.rows_pad; p.b_rows_pad = B.rows_pad;
+  p.planes = A.planes;
+  p.nterms = 0;
+  for (int i = 0; i < A.planes; ++i)
+    for (int j = 0; j < A.planes; ++j)
+      if (i + j < A.planes) {
+        p.term_a[p.nterms] = (unsigned char)i;
+        p.term_b[p.nterms] = (unsigned char)j;
+        ++p.nterms;
+      }
+  const uint32_t fmt = A.fp16 ? 0u : 1u;  // operand format: 0 = fp16, 1 = bf16
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+  const int stage_bytes = A.planes * 2 * PLANE_TILE_BYTES;
+  int stages = (192 * 1024) / stage_bytes;
+  if (stages > 3) stages = 3;  // one-plane GEMMs: 97 KB per CTA, so two CTAs share an SM and overlap epilogue with MMA
+  p.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  dim3 grid((unsigned)ceil_div(d.N, TILE_N), (unsigned)ceil_div(d.M, TILE_M), (unsigned)d.batch);
+  umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
+  MQ_LAUNCH_CHECK();
+  return MQ_OK;
+}
+
+}  // namespace
+
+size_t engine_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split) {
+  if (math != MQ_MATH_TENSOR) return 0;
+  const size_t kp = (size_t)pad_to((int)K, SLAB_K);
+  const size_t a = (size_t)split * (size_t)pad_to((int)M, TILE_M) * kp * 2;
+  const size_t b = (size_t)split * (size_t)pad_to((int)N, TILE_N) * kp * 2;
+  return align_up(a, 256) + align_up(b, 256);
+}
+
+int gemm_tensor_f32(const GemmDesc& d, int split, Workspace ws, cudaStream_t st) {
+  if (d.M <= 0 || d.N <= 0 || d.batch <= 0) return MQ_OK;
+  MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "tensor engine: split must be 1, 2 or 3 (got %d)", split);
+  PlaneSet A, B;
+  // A planes [m][k]: the k extent follows the ragged N when k_follows_n is set
+  MQ_TRY(make_planes(d.A, MQ_F32, d.a_rs, d.a_cs, d.a_bs, d.M, d.K, d.batch, split, 0, 0,
+                     d.k_follows_n ? d.n_total : 0, d.k_follows_n ? d.n_step : 0, ws, &A, st));
+  const bool same = d.A == d.B && d.a_rs == d.b_cs && d.a_cs == d.b_rs && d.M == d.N && d.batch == 1 && !d.n_step;
+  if (same) {
+    B = A;  // symmetric rank-k update: B^T is A
+  } else {
+    // B planes [n][k] = B[k][n]
+    MQ_TRY(make_planes(d.B, MQ_F32, d.b_cs, d.b_rs, d.b_bs, d.N, d.K, d.batch, split, d.n_step ? d.n_total : 0, d.n_step,
+                       d.k_follows_n ? d.n_total : 0, d.k_follows_n ? d.n_step : 0, ws, &B, st));
+  }
+  return launch_umma(d, A, B, st);
+}
+
+size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, int split) {
+  const size_t planes = x_dtype == MQ_F32 ? (size_t)split : 1;
+  return align_up(planes * (size_t)pad_to((int)C, TILE_M) * (size_t)pad_to((int)(m > 0 ? m : 1), SLAB_K) * 2, 256);
+}
+
+int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
+                         float alpha, int split, Workspace& ws, cudaStream_t st) {
+  MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "mq_hessian_accum: split must be 1, 2 or 3 (got %d)", split);
+  GemmDesc g;
+  g.C = H; g.ldc = ldh;
+  g.M = (int)C; g.N = (int)C; g.K = (int)m;
+  g.alpha = alpha; g.beta = beta;
+  g.upper_tiles_only = 1;
+  PlaneSet A;
+  if (m > 0) {
+    // planes of X^T: row = channel, k = token
+    MQ_TRY(make_planes(X, x_dtype, 1, ldx, 0, (int)C, (int)m, 1, split, 0, 0, 0, 0, ws, &A, st));
+  } else {
+    // nothing to add: only the beta scaling remains, done by the epilogue on an empty K range
+    A.planes = 1; A.rows_pad = pad_to((int)C, TILE_M); A.K_pad = SLAB_K; A.total_rows = A.rows_pad;
+    A.base = ws.take<uint16_t>((size_t)A.rows_pad * SLAB_K);
+    MQ_REQUIRE(A.base, MQ_ERR_WORKSPACE, "mq_hessian_accum: workspace too small");
+  }
+  MQ_TRY(launch_umma(g, A, A, st));
+  return mirror_upper_to_lower(H, C, ldh, st);
+}
+
+}  // namespace mq
+
+extern "C" int mq_engine_fault(int* host_out) {
+  using namespace mq;
+  MQ_REQUIRE(host_out, MQ_ERR_ARGUMENT, "mq_engine_fault: null pointer");
+  MQ_CUDA(cudaMemcpyFromSymbol(host_out, g_engine_fault, sizeof(int)));
+  return MQ_OK;
+}

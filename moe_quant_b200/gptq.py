@@ -1,0 +1,302 @@
+"""GPTQ handle with the constructor, attributes and methods of src.gptq.GPTQ
+(src/gptq.py:22-243), driving the sm_100a engine.
+
+What differs from the reference, by design:
+  * `update` feeds the activation batch to the Hessian kernel in its own dtype;
+    no fp32 copy of X is made (src/gptq.py:97).
+  * `quantize` is one C-ABI call: the NaN / dead-channel / zero-column checks run
+    on the device and are read back once, together, after the layer is done.
+  * `quantize_tied` quantizes handles that share a Hessian with ONE factorisation;
+    the reference refactors the same matrix per tied handle (src/gptq.py:189).
+  * distributed handles: the Hessian is summed with token-count weights, so ranks
+    may hold different numbers of tokens (the reference's plain AVG, src/gptq.py:139,
+    is exact only for equal counts).
+"""
+from __future__ import annotations
+
+from enum import Enum
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+from torch.nn.modules.conv import _ConvNd
+
+from . import dist_utils, model_utils, ops
+from ._lib import MoeQuantError
+
+
+class QuantizationOrder(Enum):
+    DEFAULT = "default"
+    ACTIVATION = "activation"
+
+
+class GPTQ:
+    def __init__(
+        self,
+        layer: nn.Module,
+        group_size: Optional[int] = None,
+        sym: bool = False,
+        rel_damp: float = 1e-2,
+        block_size: Optional[int] = None,
+        quantization_order: str = "default",
+        quantization_scale: str = "absmax",
+        is_distributed: bool = False,
+        tied_gptq_handle: Optional["GPTQ"] = None,
+        precision: Optional[ops.Precision] = None,
+    ):
+        self._validate_layer(layer)
+        self.layer = layer
+        self.W = layer.weight
+        self.d_row, self.d_col = model_utils.get_number_of_rows_and_cols(layer)
+        self.sym = sym
+        self.group_size = group_size
+        self.rel_damp = rel_damp
+        self.block_size = block_size or self.d_col
+        self.quantization_order = QuantizationOrder(quantization_order)
+        self.quantization_scale = quantization_scale
+        self.W_device = self.W.device
+        self.W_dtype = self.W.dtype
+        self.W_shape = self.W.shape
+        self.H: Optional[Tensor] = None
+        self.num_samples = 0
+        self.is_distributed = is_distributed
+        self.tied_gptq_handle = tied_gptq_handle
+        self.num_tied_handles = 0
+        if tied_gptq_handle is not None:
+            tied_gptq_handle.num_tied_handles += 1
+        self.issue_zero_samples = False
+        self.issue_nan_hessian = False
+        self.issue_non_invertible = False
+        self.precision = precision
+        self.pre_step_completed = False
+        self._hessian_ready = False   # True once H has been masked and damped
+        self._uhat: Optional[Tensor] = None
+        self._was_reset = False
+
+    @staticmethod
+    def _validate_layer(layer) -> None:
+        assert isinstance(layer, (nn.Linear, _ConvNd)), "OBC supports only linear and convolutional layers."
+
+    def has_hessian_issues(self) -> bool:
+        return any([self.issue_zero_samples, self.issue_nan_hessian, self.issue_non_invertible])
+
+    # ------------------------------------------------------------------ Hessian
+    @torch.no_grad()
+    def update(self, input: Tensor) -> None:
+        """H <- n/(n+m) H + 2/(n+m) X^T X (src/gptq.py:74-105)."""
+        if self.H is None:
+            self.H = torch.zeros((self.d_col, self.d_col), device=input.device, dtype=torch.float32)
+            self._was_reset = False
+        if isinstance(self.layer, nn.Linear):
+            x = input.reshape(-1, input.shape[-1])
+        else:
+            unfold = nn.Unfold(self.layer.kernel_size, dilation=self.layer.dilation, padding=self.layer.padding,
+                               stride=self.layer.stride)
+            x = unfold(input).transpose(1, 2).flatten(0, 1)
+        if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            x = x.float()
+        m = x.shape[0]
+        if m == 0:
+            return
+        beta = self.num_samples / (self.num_samples + m)
+        alpha = 2.0 / (self.num_samples + m)
+        ops.hessian_accum(self.H, x, beta, alpha, self.precision)
+        self.num_samples += m
+
+    @property
+    def tokens_collected(self) -> int:
+        return self.num_samples
+
+    def reset(self) -> None:
+        """src/gptq.py:111-120.  A Hessian shared with tied handles (and its cached factor) is
+        released when the owner and every tied handle have been reset; the reference keeps it
+        until the owner object itself is dropped."""
+        self.W = self.layer.weight
+        owner = self.tied_gptq_handle
+        if owner is not None:
+            self.H = None
+            if not self._was_reset:
+                owner.num_tied_handles -= 1
+            if owner.num_tied_handles == 0 and owner._was_reset:
+                owner._drop_hessian()
+        elif self.num_tied_handles == 0:
+            self._drop_hessian()
+        self._was_reset = True
+        self.num_samples = 0
+        self.pre_step_completed = False
+
+    def _drop_hessian(self) -> None:
+        self.H = None
+        self._uhat = None
+        self._hessian_ready = False
+
+    # ------------------------------------------------------------------ pre-step
+    @torch.no_grad()
+    def quantization_pre_step(self) -> None:
+        """Host part of src/gptq.py:123-154: Hessian fallback and cross-rank reduction.
+        The NaN / dead-channel fixes and the fp32 clone of W happen inside the kernels."""
+        reduce_if_needed = True
+        if self.H is None:
+            if self.tied_gptq_handle is not None:
+                self.H = self.tied_gptq_handle.H
+            if self.H is None:
+                self.H = torch.eye(self.d_col, device=self.W_device, dtype=torch.float32)
+                self.issue_zero_samples = True
+            reduce_if_needed = False
+        if self.is_distributed and reduce_if_needed and dist_utils.is_dist_available_and_initialized():
+            self._reduce_hessian()
+        self.pre_step_completed = True
+
+    def _reduce_hessian(self) -> None:
+        """Token-weighted mean of the per-rank running means.  With equal token counts this
+        is the reference's all_reduce(AVG) (src/gptq.py:139)."""
+        n = torch.tensor([float(self.num_samples)], device=self.H.device, dtype=torch.float64)
+        dist.all_reduce(n, op=dist.ReduceOp.SUM)
+        total = float(n.item())
+        if total > 0:
+            self.H.mul_(self.num_samples / total)
+            dist.all_reduce(self.H, op=dist.ReduceOp.SUM)
+
+    # ------------------------------------------------------------------ quantize
+    def _group(self) -> int:
+        g = self.group_size or self.d_col
+        if self.d_col % g != 0:
+            raise MoeQuantError(f"group_size {g} does not divide d_col {self.d_col}")
+        return g
+
+    def _weight_2d(self) -> Tensor:
+        w = self.layer.weight.detach()
+        return w.flatten(1, -1) if w.dim() > 2 else w
+
+    def _absorb_flags(self, flags: Tensor) -> None:
+        nan, _dead, _zero, not_pd = flags.tolist()   # the one host sync of a layer
+        self.issue_nan_hessian = self.issue_nan_hessian or bool(nan)
+        self.issue_non_invertible = self.issue_non_invertible or bool(not_pd)
+
+    @torch.no_grad()
+    def _quantize(self, bits: int) -> Tuple[Tensor, Tensor, Tensor]:
+        if not self.sym:
+            raise MoeQuantError("only symmetric quantization is implemented (the reference's asymmetric grid is broken)")
+        d_row, d_col, device, dtype = self.d_row, self.d_col, self.W_device, self.W_dtype
+        g = self._group()
+        n_groups = d_col // g
+        main = dist_utils.is_main() or not self.is_distributed
+        if main:
+            if self.quantization_order == QuantizationOrder.ACTIVATION:
+                qweight, scale = self._quantize_act_order(bits, g)
+            else:
+                qweight, scale = self._quantize_default(bits, g)
+            scale = scale.to(dtype)
+            zero = torch.full_like(scale, (2 ** bits) / 2)
+        else:
+            qweight = torch.empty(d_row, d_col, device=device, dtype=torch.uint8)
+            scale = torch.empty(d_row, n_groups, device=device, dtype=dtype)
+            zero = torch.empty(d_row, n_groups, device=device, dtype=dtype)
+        if self.is_distributed and dist_utils.is_dist_available_and_initialized():
+            dist.barrier()
+            dist.broadcast(qweight, src=0)
+            dist.broadcast(scale, src=0)
+            dist.broadcast(zero, src=0)
+        return qweight, scale, zero
+
+    def _quantize_default(self, bits: int, g: int) -> Tuple[Tensor, Tensor]:
+        W = self._weight_2d()
+        shares_hessian = self.num_tied_handles > 0 or self.tied_gptq_handle is not None
+        if not shares_hessian:
+            codes, scales, _, flags = ops.quantize_layer([W], self.H, g, bits, self.rel_damp, precision=self.precision)
+            self._hessian_ready = True
+            self._absorb_flags(flags)
+            return codes[0], scales[0]
+        # Handles that share a Hessian and are quantized one call at a time (the reference
+        # driver's loop, quant.py:351-387): regularise H once, factor it once, keep the factor
+        # until the last of them is reset.
+        Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
+        owner = self.tied_gptq_handle if self.tied_gptq_handle is not None else self
+        if not owner._hessian_ready:
+            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
+            owner._hessian_ready = True
+            self._absorb_flags(flags)
+        if owner._uhat is None:
+            owner._uhat, flags, _ = ops.hinv_upper(self.H.clone(), self.precision)
+            self._absorb_flags(flags)
+        self._hessian_ready = True
+        scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
+        codes, _ = ops.gptq_sweep(Wf, owner._uhat, scale, None, g, self.d_col // g, 1, bits, self.W_dtype,
+                                  precision=self.precision)
+        return codes, scale
+
+    def _quantize_act_order(self, bits: int, g: int) -> Tuple[Tensor, Tensor]:
+        """Activation ordering (src/gptq.py:180-187): columns sorted by decreasing diag(H); each
+        column keeps the scale of its original group."""
+        W = self._weight_2d()
+        Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
+        if not self._hessian_ready:
+            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
+            self._hessian_ready = True
+            self._absorb_flags(flags)
+        scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
+        perm = torch.argsort(self.H.diag(), descending=True)
+        Hp = self.H[perm][:, perm].contiguous()
+        U, flags, _ = ops.hinv_upper(Hp, self.precision)
+        self._absorb_flags(flags)
+        Wp = Wf[:, perm].contiguous()
+        sp = scale.repeat_interleave(g, dim=-1)[:, perm].contiguous()
+        codes_p, _ = ops.gptq_sweep(Wp, U, sp, None, 1, self.d_col, 1, bits, self.W_dtype, precision=self.precision)
+        codes = torch.empty_like(codes_p)
+        codes[:, perm] = codes_p
+        return codes, scale
+
+    def quantize(self, bits: int | float) -> Tuple[Tensor, Tensor, Tensor]:
+        self.quantization_pre_step()
+        return self._quantize(int(bits))
+
+    @torch.no_grad()
+    def _get_hessian_inverse(self) -> Tensor:
+        """Seam of src/gptq.py:220-243: mask, damp (once per Hessian) and factor."""
+        Wf = self._weight_2d().float().contiguous()
+        if not self._hessian_ready:
+            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
+            self._hessian_ready = True
+            self._absorb_flags(flags)
+        U, flags, _ = ops.hinv_upper(self.H.clone(), self.precision)
+        self._absorb_flags(flags)
+        return U
+
+
+@torch.no_grad()
+def quantize_tied(handles: Sequence[GPTQ], bits: int) -> List[Tuple[Tensor, Tensor, Tensor]]:
+    """Quantizes handles that share one Hessian (gate_proj/up_proj of an expert,
+    quant.py:258-262) with a single factorisation.  handles[0] owns H; the others were
+    built with tied_gptq_handle=handles[0].  Returns one (qweight, scale, zero) per handle,
+    identical to calling handle.quantize(bits) on each in turn."""
+    owner = handles[0]
+    for h in handles[1:]:
+        if h.tied_gptq_handle is not owner:
+            raise MoeQuantError("quantize_tied: every handle after the first must be tied to the first")
+    if owner.quantization_order != QuantizationOrder.DEFAULT or not owner.sym:
+        return [h.quantize(bits) for h in handles]
+    owner.quantization_pre_step()
+    for h in handles[1:]:
+        h.quantization_pre_step()
+    if owner.is_distributed and not dist_utils.is_main():
+        return [h._quantize(bits) for h in handles]
+    g = owner._group()
+    codes, scales, _, flags = ops.quantize_layer([h._weight_2d() for h in handles], owner.H, g, int(bits),
+                                                 owner.rel_damp, precision=owner.precision)
+    owner._hessian_ready = True
+    owner._absorb_flags(flags)
+    out = []
+    for h, q, s in zip(handles, codes, scales):
+        h._hessian_ready = True
+        h.issue_nan_hessian = owner.issue_nan_hessian
+        h.issue_non_invertible = owner.issue_non_invertible
+        s = s.to(h.W_dtype)
+        z = torch.full_like(s, (2 ** int(bits)) / 2)
+        if h.is_distributed and dist_utils.is_dist_available_and_initialized():
+            dist.barrier()
+            for t in (q, s, z):
+                dist.broadcast(t, src=0)
+        out.append((q, s, z))
+    return out

@@ -1,0 +1,240 @@
+"""Parity of every CUDA entry point (called through the C ABI) with the oracle and
+with the fixtures written by the reference's own code.
+
+Tolerances (from the stated parity bar): packed words and dequantized values
+bit-exact; scales exact (<= 1e-3 relative allowed); >= 99.5 % of the int4 codes equal;
+Hessian-weighted reconstruction error within 1 % relative.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from moe_quant_b200 import ops, synthetic
+from moe_quant_b200._lib import MATH_FP32, MATH_TENSOR, MoeQuantError
+from oracle import gptq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+CODE_AGREEMENT = 0.995
+SCALE_RTOL = 1e-3
+RECON_RTOL = 0.01
+
+
+@pytest.fixture(params=["fp32", "tensor"])
+def precision(request):
+    math = MATH_FP32 if request.param == "fp32" else MATH_TENSOR
+    return ops.Precision(math=math, split_hessian=3, split_hinv=3, split_sweep=3)
+
+
+# ------------------------------------------------------------------ packing
+def test_pack_golden_vectors(cuda):
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "pack_int4.npz"))
+    for key in z.files:
+        if key.startswith("v_"):
+            v = torch.from_numpy(z[key])
+            got = ops.pack_int4((v + 8).to(torch.uint8).to(cuda)).cpu()
+            assert torch.equal(got, torch.from_numpy(z["p_" + key[2:]])), key
+
+
+@pytest.mark.parametrize("shape", [(1, 16), (7, 2048), (33, 264), (5, 13), (128, 7168), (3, 1), (0, 64), (4, 0)])
+def test_pack_random_shapes(cuda, shape):
+    g = torch.Generator().manual_seed(shape[0] * 131 + shape[1])
+    codes = torch.randint(0, 16, shape, generator=g, dtype=torch.uint8)
+    got = ops.pack_int4(codes.to(cuda)).cpu()
+    want = O.pack_to_int32(codes.to(torch.int8) - 8, 4) if codes.numel() else torch.empty(shape[0], (shape[1] + 7) // 8, dtype=torch.int32)
+    assert got.shape == want.shape and torch.equal(got, want)
+
+
+def test_pack_with_zero_points(cuda):
+    g = torch.Generator().manual_seed(5)
+    codes = torch.randint(0, 16, (9, 64), generator=g, dtype=torch.uint8)
+    zero = torch.randint(6, 10, (9, 2), generator=g, dtype=torch.int8)
+    shifted = codes.to(torch.int8) - zero.repeat_interleave(32, dim=-1)
+    shifted = shifted.clamp(-8, 7)
+    codes = (shifted + zero.repeat_interleave(32, dim=-1)).to(torch.uint8)
+    got = ops.pack_int4(codes.to(cuda), zero.to(cuda), 32).cpu()
+    assert torch.equal(got, O.pack_to_int32(shifted, 4))
+
+
+def test_pack_unpack_round_trip_full_size(cuda):
+    """Property at the full down_proj size: unpacking the words gives the codes back."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    codes = torch.randint(0, 16, (7168, 2048), generator=g, dtype=torch.uint8, device=cuda)
+    words = ops.pack_int4(codes)
+    shifts = torch.arange(8, device=cuda, dtype=torch.int32) * 4
+    back = ((words.unsqueeze(-1) >> shifts) & 0xF).reshape(7168, 2048).to(torch.uint8)
+    assert torch.equal(back, codes)
+
+
+def test_pack_golden_layers(cuda, golden):
+    got = ops.pack_int4(golden.t("qweight").to(cuda)).cpu()
+    assert torch.equal(got, golden.t("weight_packed"))
+
+
+# ------------------------------------------------------------------ dequantize
+def test_dequantize_golden(cuda, golden):
+    q = golden.t("qweight").to(cuda)
+    s = golden.t("scale", typed=True).to(cuda)
+    zr = golden.t("zero", typed=True).to(cuda)
+    got = ops.dequantize(q, s, zr, golden.group, 4, golden.dtype).cpu()
+    assert torch.equal(got.float(), golden.t("dequantized", typed=True).float())
+    got2 = ops.dequantize(q, s, None, golden.group, 4, golden.dtype).cpu()
+    assert torch.equal(got2.float(), got.float())
+
+
+# ------------------------------------------------------------------ Hessian
+def test_hessian_accum_golden(cuda, golden, precision):
+    C = golden.W.shape[1]
+    H = torch.zeros(C, C, dtype=torch.float32, device=cuda)
+    n = 0
+    for k, x in enumerate(golden.batches):
+        m = x.shape[0]
+        ops.hessian_accum(H, x.to(cuda), n / (n + m), 2.0 / (n + m), precision)
+        n += m
+        if k == 0 and len(golden.batches) > 1:
+            torch.testing.assert_close(H.cpu(), golden.t("H_after0"), rtol=2e-5, atol=1e-5)
+    Hc = H.cpu()
+    torch.testing.assert_close(Hc, golden.t("H_final"), rtol=2e-5, atol=1e-5)
+    assert torch.equal(Hc, Hc.t()), "both triangles must hold the same numbers"
+
+
+@pytest.mark.parametrize("m,C,dtype", [(1, 128, torch.float32), (37, 256, torch.bfloat16), (513, 384, torch.float16),
+                                       (1000, 1024, torch.bfloat16), (300, 2048, torch.float32), (0, 128, torch.bfloat16)])
+def test_hessian_accum_ragged(cuda, precision, m, C, dtype):
+    x = synthetic.activations(max(m, 1), C, 3, dtype)[:m]
+    H0 = synthetic.layer_weight(C, C, 9)
+    H0 = (H0 + H0.t()).contiguous()
+    H = H0.clone().to(cuda)
+    ops.hessian_accum(H, x.to(cuda), 0.25, 0.5, precision)
+    want = 0.25 * H0.double() + 0.5 * (x.double().t() @ x.double())
+    err = (H.cpu().double() - want).abs().max() / want.abs().max()
+    assert float(err) < 5e-6   # tensor-core fp32 accumulation truncates; fp32 FMA path reaches ~3e-7
+
+
+# ------------------------------------------------------------------ prepare
+def test_prepare_golden(cuda, golden):
+    H = golden.t("H_final").clone().to(cuda)
+    W = golden.W.float().to(cuda)
+    flags = ops.hessian_prepare(H, W, 1e-2).cpu().tolist()
+    torch.testing.assert_close(H.cpu(), golden.t("H_damped"), rtol=1e-6, atol=1e-7)
+    dead = len(golden.meta.get("dead", ()))
+    zero_w = len(golden.meta.get("zero_w", ()))
+    assert flags == [0, dead, dead + zero_w, 0]
+    for j in golden.meta.get("dead", ()):
+        assert float(W[:, j].abs().max()) == 0.0
+
+
+def test_prepare_nan_hessian_becomes_identity(cuda):
+    H = torch.eye(64, device=cuda) * 3
+    H[5, 7] = float("nan")
+    flags = ops.hessian_prepare(H, None, 0.5).cpu().tolist()
+    assert flags[0] == 1
+    torch.testing.assert_close(H.cpu(), torch.eye(64) * 1.5)
+
+
+# ------------------------------------------------------------------ scales
+def test_scales_golden(cuda, golden):
+    _, Wf, _, _ = O.pre_step(golden.t("H_final").clone(), golden.W)
+    got = ops.absmax_scales(Wf.to(cuda), golden.group, 4, golden.dtype).cpu()
+    assert torch.equal(got, golden.t("scale", typed=True).float())
+
+
+@pytest.mark.parametrize("g", [4, 8, 32, 64, 128, 256, 1024])
+def test_scales_group_sizes(cuda, g):
+    W = synthetic.layer_weight(19, 1024, 4)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        want, _, _ = O.symmetric_grid(W, g, 4, dt)
+        got = ops.absmax_scales(W.to(cuda), g, 4, dt).cpu()
+        assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------ Hessian inverse factor
+def test_hinv_golden(cuda, golden, precision):
+    U, flags, _ = ops.hinv_upper(golden.t("H_damped").clone().to(cuda), precision)
+    assert flags.cpu().tolist()[3] == 0
+    Uc = U.cpu()
+    assert float(Uc.tril(-1).abs().max()) == 0.0
+    assert torch.equal(Uc.diag(), torch.ones(Uc.shape[0]))
+    torch.testing.assert_close(Uc, golden.t("Uhat"), rtol=2e-3, atol=2e-5)
+
+
+@pytest.mark.parametrize("C", [128, 136, 640, 1000, 1536])
+def test_hinv_sizes(cuda, precision, C):
+    x = synthetic.activations(C // 2 + 11, C, 21)
+    H, _ = O.hessian_update(None, 0, x)
+    W = synthetic.layer_weight(8, C, 2)
+    want, failed = O.hessian_inverse(H, W, 1e-2)  # damps H in place
+    assert not failed
+    U, flags, _ = ops.hinv_upper(H.clone().to(cuda), precision)
+    assert flags.cpu().tolist()[3] == 0
+    rel = (U.cpu() - want).norm() / want.norm()
+    assert float(rel) < 2e-4
+
+
+def test_hinv_not_positive_definite_gives_identity(cuda, precision):
+    H = torch.eye(256)
+    H[200, 200] = -1.0
+    U, flags, _ = ops.hinv_upper(H.to(cuda), precision)
+    assert flags.cpu().tolist()[3] == 201
+    assert torch.equal(U.cpu(), torch.eye(256))
+
+
+def test_inv_sym_seam(cuda, precision):
+    from moe_quant_b200 import linalg_utils
+    x = synthetic.activations(400, 256, 8)
+    H, _ = O.hessian_update(None, 0, x)
+    H += 0.1 * torch.eye(256)
+    got = linalg_utils.inv_sym(H.to(cuda), precision).cpu().double()
+    eye = got @ H.double()
+    assert float((eye - torch.eye(256, dtype=torch.float64)).abs().max()) < 5e-3
+
+
+# ------------------------------------------------------------------ sweep
+def _grid(golden):
+    _, Wf, _, _ = O.pre_step(golden.t("H_final").clone(), golden.W)
+    scale, _, _ = O.symmetric_grid(Wf, golden.group, 4, golden.dtype)
+    return Wf, scale
+
+
+def test_sweep_with_reference_factor(cuda, golden, precision):
+    Wf, scale = _grid(golden)
+    R, C = Wf.shape
+    codes, deq = ops.gptq_sweep(Wf.to(cuda), golden.t("Uhat").to(cuda), scale.to(cuda), None, golden.group,
+                                C // golden.group, 1, 4, golden.dtype, True, precision)
+    assert O.code_agreement(codes.cpu(), golden.t("qweight")) >= 0.999
+    want = O.dequantize_linear_weight(codes.cpu(), golden.t("scale", typed=True), golden.t("zero", typed=True))
+    assert torch.equal(deq.cpu().float(), want.float())
+
+
+def test_gptq_loop_seam(cuda, golden, precision):
+    """The reference's inner seam: transposed weight, per-element scale and zero."""
+    from moe_quant_b200 import gptq_loop
+    ops.set_default_precision(precision)
+    try:
+        Wf, scale = _grid(golden)
+        g = golden.group
+        sf = scale.repeat_interleave(g, -1)
+        zf = torch.full_like(sf, 8.0)
+        wt = Wf.t().contiguous().to(cuda)
+        q = gptq_loop.gptq_loop(wt, golden.t("Uhat").to(cuda), sf.t().contiguous().to(cuda), zf.t().contiguous().to(cuda),
+                                torch.tensor(15.0, device=cuda), golden.dtype, 128)
+    finally:
+        ops.set_default_precision(ops.Precision())
+    assert q.shape == wt.shape and q.dtype == torch.float32
+    codes = q.t().contiguous().to(torch.uint8).cpu()
+    assert O.code_agreement(codes, golden.t("qweight")) >= 0.999
+    deq = O.dequantize_linear_weight(codes, golden.t("scale", typed=True), golden.t("zero", typed=True))
+    assert torch.equal(wt.t().cpu().to(golden.dtype).float(), deq.float())
+
+
+# ------------------------------------------------------------------ argument errors (no fallback, loud failures)
+def test_cpu_tensor_is_rejected():
+    with pytest.raises(MoeQuantError):
+        ops.pack_int4(torch.zeros(4, 8, dtype=torch.uint8))
+
+
+def test_bad_group_is_rejected(cuda):
+    with pytest.raises(MoeQuantError):
+        ops.absmax_scales(torch.zeros(4, 96, device=cuda), 64, 4, torch.float32)

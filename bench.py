@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""GPTQ layers/sec on the DeepSeek-V3 routed-expert gate_proj shape (2048 x 7168, 4 bit, g128).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1).  Routed experts
+are expert-parallel: every rank quantizes its own experts and nothing crosses NVLink, so the
+job is weak-scaled and `value` is (layers all ranks quantized) / (max-over-ranks time).
+
+A step is one `GPTQ.quantize(4)` call on one expert's gate_proj whose Hessian is already
+accumulated on the device: pre-step, scales, Hessian-inverse factor, column sweep, codes out.
+Steps rotate over distinct experts (weight 29 MB + Hessian 205 MB each, larger than L2).
+
+Printed JSON (one line, rank 0):
+  value      layers/s with inputs resident in HBM
+  e2e        layers/s through the public handle with HOST buffers: weight and calibration
+             activations copied from pinned memory, Hessian accumulated, layer quantized,
+             codes and scales copied back, every step
+  roofline   the kernel that takes the largest share of a step, timed with CUDA events on
+             its launching stream by the library's profiling hooks in a separate pass
+  cpu_baseline  the CPU oracle (a port of the reference's torch path) on this box's cores
+`--impl reference` times that CPU path alone, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+R, C, TOKENS, GROUP, BITS = 2048, 7168, 4096, 128, 4
+WORKLOAD = "deepseek_v3_routed_expert_gate_proj_2048x7168_bf16_g128 (one rank's expert shard, Hessian resident)"
+METRIC = "GPTQ layers/sec (2048x7168, 4b g128)"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=p["hbm_gbs"], tensor_burst=p["bf16_tflops"], tensor_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, tensor_burst=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                           "samples": len(sm)}
+
+
+def _dist():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local
+
+
+# ---------------------------------------------------------------------------- reference arm / CPU baseline
+def cpu_layers_per_s(steps: int, warmup: int, threads: int, dtype=torch.bfloat16):
+    """The oracle's GPTQ.quantize on one 2048 x 7168 layer per step, Hessian pre-accumulated."""
+    from moe_quant_b200 import synthetic
+    from oracle import gptq_oracle as O
+
+    torch.set_num_threads(threads)
+    W = synthetic.layer_weight(R, C, 0, dtype)
+    X = synthetic.activations(TOKENS, C, 0, dtype)
+    t0 = time.perf_counter()
+    H, _ = O.hessian_update(None, 0, X)
+    t_h = time.perf_counter() - t0
+    times = []
+    for i in range(warmup + steps):
+        Hc = H.clone()
+        t0 = time.perf_counter()
+        O.quantize_layer(W, Hc, bits=BITS, group_size=GROUP, rel_damp=1e-2, block_size=128)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    total = sum(times)
+    return steps / total, total / steps * 1e3, 2.0 * TOKENS * C * C / t_h / 1e12
+
+
+def run_reference(args):
+    world, rank, _ = _dist()
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    steps, warmup = args.steps, args.warmup
+    value, ms, h_tflops = cpu_layers_per_s(steps, warmup, cores)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "layers/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": "one full 2048x7168 layer per step, Hessian from 4096 tokens"},
+        "cpu_baseline": {"value": value, "unit": "layers/s", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full layers after {warmup} warm-up, torch CPU oracle, {cores} threads"},
+        "hessian_tflops_2nc2_cpu": h_tflops,
+        "e2e": {"value": value, "unit": "layers/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------- B200 arm
+def run_b200(args):
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    from moe_quant_b200 import GPTQ, _lib, ops, synthetic
+
+    world, rank, local = _dist()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this engine has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    n_experts = 4
+    seed = 1234 + 100 * rank
+
+    # ---- this rank's experts: weights and Hessians resident in HBM (set-up, untimed)
+    counts = synthetic.ragged_expert_counts(32 * 1024, 256, 8, seed)   # ragged top-8 routing of 32k tokens
+    weights, hessians, tokens = [], [], []
+    for e in range(n_experts):
+        W = synthetic.layer_weight(R, C, seed + e, torch.bfloat16).to(dev)
+        m = int(counts[(rank * n_experts + e) % 256].clamp(min=256, max=4 * TOKENS))
+        g = torch.Generator(device=dev).manual_seed(seed + e)
+        chan = torch.exp(torch.randn(C, generator=g, device=dev))
+        X = (torch.randn(m, C, generator=g, device=dev) * chan).to(torch.bfloat16)
+        H = torch.zeros(C, C, dtype=torch.float32, device=dev)
+        ops.hessian_accum(H, X, 0.0, 2.0 / m)
+        weights.append(W)
+        hessians.append(H)
+        tokens.append(m)
+        del X
+
+    def make_handles(n):
+        hs = []
+        for i in range(n):
+            e = i % n_experts
+            layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
+            layer.weight = nn.Parameter(weights[e], requires_grad=False)
+            h = GPTQ(layer, GROUP, True, 1e-2, 128)
+            h.H = hessians[e].clone()
+            h.num_samples = tokens[e]
+            hs.append(h)
+        return hs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: K quantize() calls
+    handles = make_handles(warmup + steps)
+    for h in handles[:warmup]:
+        h.quantize(BITS)
+    barrier()
+    launches0 = _lib.lib().mq_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        results = [h.quantize(BITS) for h in handles[warmup:]]
+        ev1.record()
+        barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = _lib.lib().mq_launch_count() - launches0
+    issues = sum(h.has_hessian_issues() for h in handles)
+    fault = _lib.engine_fault()
+    del handles, results
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * steps / (ms_max / 1e3)
+
+    # ---- per-kernel pass (same work, events around every launch of the hot kernels)
+    prof_handles = make_handles(min(steps, 4))
+    torch.cuda.synchronize()
+    _lib.profile_begin()
+    for h in prof_handles:
+        h.quantize(BITS)
+    prof = _lib.profile_end()
+    del prof_handles
+    peaks = _peaks()
+    kinds = {k: v for k, v in prof.items() if v["launches"]}
+    top = max(kinds, key=lambda k: kinds[k]["ms"]) if kinds else None
+    roofline, shares = None, {}
+    if top:
+        tot = sum(v["ms"] for v in kinds.values())
+        shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
+        v = kinds[top]
+        if top in ("umma_gemm", "simt_gemm"):
+            achieved = v["work"] / (v["ms"] / 1e3) / 1e12
+            roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"], "traffic": None,
+                        "issued_tflops": v["work2"] / (v["ms"] / 1e3) / 1e12,
+                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
+                        "peak_source": peaks["source"] + " (sustained bf16)"}
+        else:
+            achieved = v["work"] / (v["ms"] / 1e3) / 1e9
+            roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm"], "traffic": None, "avg_launch_us": v["ms"] / v["launches"] * 1e3,
+                        "peak_source": peaks["source"]}
+
+    # ---- Hessian accumulation rate (the second half of the headline metric)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    X = (torch.randn(TOKENS, C, generator=g, device=dev)).to(torch.bfloat16)
+    Hs = torch.zeros(C, C, dtype=torch.float32, device=dev)
+    for _ in range(3):
+        ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
+    e1.record()
+    torch.cuda.synchronize()
+    h_ms = e0.elapsed_time(e1) / 10
+    del Hs
+
+    # ---- end to end through the handle with host buffers
+    Wh = [w.cpu().pin_memory() for w in weights]
+    Xh = synthetic.activations(TOKENS, C, seed, torch.bfloat16).pin_memory()
+    q_host = torch.empty(R, C, dtype=torch.uint8).pin_memory()
+    s_host = torch.empty(R, C // GROUP, dtype=torch.bfloat16).pin_memory()
+    h2d = Wh[0].numel() * 2 + Xh.numel() * 2
+    d2h = q_host.numel() + s_host.numel() * 2
+
+    def e2e_step(i):
+        W = Wh[i % n_experts].to(dev, non_blocking=True)
+        Xd = Xh.to(dev, non_blocking=True)
+        layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
+        layer.weight = nn.Parameter(W, requires_grad=False)
+        h = GPTQ(layer, GROUP, True, 1e-2, 128)
+        h.update(Xd)
+        q, s, _z = h.quantize(BITS)
+        q_host.copy_(q, non_blocking=True)
+        s_host.copy_(s, non_blocking=True)
+        h.reset()
+
+    e2e_steps = steps
+    for i in range(warmup):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * e2e_steps / (float(t.item()) / 1e3)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        v, ms, _ = cpu_layers_per_s(2, 1, cores)
+        cpu = {"value": v, "unit": "layers/s", "cores": cores, "kind": "port",
+               "sample": f"2 full 2048x7168 layers after 1 warm-up ({ms:.0f} ms each), torch CPU oracle, {cores} threads"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "layers/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "experts_rotated": n_experts, "tokens_per_expert": tokens,
+                       "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
+                       "parallelism": f"ep{world}", "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
+            "roofline": roofline, "kernel_time_shares": shares,
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "layers/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "clocks": clocks.result,
+            "hessian_accum": {"ms": h_ms, "tflops_2NC2": 2.0 * TOKENS * C * C / h_ms / 1e9,
+                              "tflops_unique": TOKENS * C * (C + 1) / h_ms / 1e9, "tokens": TOKENS, "dtype": "bf16"},
+            "hessian_issues": int(issues), "engine_fault": int(fault),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,11 +65,26 @@ typedef struct {
 int mq_abi_version(void);
 const char* mq_last_error(void);
 
+/* Number of CUDA kernels this library has launched in this process (host-side counter). */
+long long mq_launch_count(void);
+
 /* Every device-side wait in the tensor-core kernels is bounded.  If one ever expires the
  * kernel records a non-zero code, frees its resources and returns; results of that call are
  * then invalid.  This copies the current device's code to *host_out (0 = healthy).  It
  * synchronises the device, so call it where a synchronisation is acceptable.  */
 int mq_engine_fault(int* host_out);
+
+/* Per-kernel timing for benchmarks: between mq_profile_begin() and mq_profile_end() every
+ * launch of the kernel families below is bracketed by CUDA events on its own stream.
+ * mq_profile_end synchronises the device and fills four arrays of MQ_PROFILE_KINDS entries:
+ * launches, summed milliseconds, and two work figures (GEMM kinds: algorithmic flop and
+ * issued tensor flop; sweep: algorithmic bytes and flop; split/pack: bytes).
+ * Not thread-safe; meant for one benchmarking thread.  */
+#define MQ_PROFILE_KINDS 8
+enum { MQ_PROF_UMMA_GEMM = 0, MQ_PROF_SIMT_GEMM = 1, MQ_PROF_SWEEP_TILE = 2, MQ_PROF_CHOL_DIAG = 3,
+       MQ_PROF_TRSM = 4, MQ_PROF_SPLIT = 5, MQ_PROF_PACK = 6, MQ_PROF_OTHER = 7 };
+int mq_profile_begin(void);
+int mq_profile_end(int64_t* launches, double* milliseconds, double* work, double* work2);
 
 /* ------------------------------------------------------------------ a2
  * H <- beta*H + alpha*X^T X, H (C,C) fp32 symmetric, X (m,C) of x_dtype.

@@ -24,7 +24,11 @@ _DTYPES = {torch.float32: MQ_F32, torch.bfloat16: MQ_BF16, torch.float16: MQ_F16
 SIGNATURES = {
     "mq_abi_version": (c_int, []),
     "mq_last_error": (c_char_p, []),
+    "mq_launch_count": (ctypes.c_longlong, []),
     "mq_engine_fault": (c_int, [ctypes.POINTER(c_int)]),
+    "mq_profile_begin": (c_int, []),
+    "mq_profile_end": (c_int, [ctypes.POINTER(c_int64), ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
+                               ctypes.POINTER(ctypes.c_double)]),
     "mq_hessian_accum": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float, c_float,
                                  c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "mq_hessian_accum_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int, c_int]),
@@ -83,6 +87,25 @@ def engine_fault() -> int:
     out = c_int(0)
     check(lib().mq_engine_fault(ctypes.byref(out)))
     return out.value
+
+
+PROFILE_KINDS = ["umma_gemm", "simt_gemm", "sweep_tile", "chol_diag", "trsm_rows", "split_planes", "pack_int4", "other"]
+
+
+def profile_begin() -> None:
+    check(lib().mq_profile_begin())
+
+
+def profile_end() -> dict:
+    """{kind: dict(launches, ms, work, work2)} for the launches since profile_begin()."""
+    n = len(PROFILE_KINDS)
+    launches = (c_int64 * n)()
+    ms = (ctypes.c_double * n)()
+    work = (ctypes.c_double * n)()
+    work2 = (ctypes.c_double * n)()
+    check(lib().mq_profile_end(launches, ms, work, work2))
+    return {k: dict(launches=int(launches[i]), ms=float(ms[i]), work=float(work[i]), work2=float(work2[i]))
+            for i, k in enumerate(PROFILE_KINDS)}
 
 
 def dtype_code(dtype: torch.dtype) -> int:

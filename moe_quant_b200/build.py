@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmoequant_sm100.so")
-SOURCES = ["api.cu", "pack.cu", "prepare.cu", "gemm_simt.cu", "hinv.cu", "sweep.cu", "umma_gemm.cu"]
+SOURCES = ["api.cu", "pack.cu", "prepare.cu", "gemm_simt.cu", "hinv.cu", "sweep.cu", "umma_gemm.cu", "profile.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",

@@ -8,6 +8,7 @@
 namespace mq {
 
 static thread_local char g_error[512] = "";
+long long g_launches = 0;
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -33,6 +34,7 @@ size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, i
 
 extern "C" int mq_abi_version(void) { return MQ_ABI_VERSION; }
 extern "C" const char* mq_last_error(void) { return mq::g_error; }
+extern "C" long long mq_launch_count(void) { return mq::g_launches; }
 
 // ---------------------------------------------------------------------------- a2
 extern "C" size_t mq_hessian_accum_workspace_bytes(int x_dtype, int64_t m, int64_t C, int math, int split) {

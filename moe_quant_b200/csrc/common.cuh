@@ -31,7 +31,12 @@ void set_error(const char* fmt, ...);
     }                                                                              \
   } while (0)
 
-#define MQ_LAUNCH_CHECK() MQ_CUDA(cudaGetLastError())
+extern long long g_launches;  // kernels launched by this library in this process
+#define MQ_LAUNCH_CHECK()         \
+  do {                            \
+    ++mq::g_launches;             \
+    MQ_CUDA(cudaGetLastError());  \
+  } while (0)
 
 #define MQ_TRY(expr)              \
   do {                            \

@@ -33,6 +33,10 @@ struct GemmDesc {
 // fp32 CUDA-core implementation; in_dtype is the element type of A and B.
 int gemm_simt(const GemmDesc& d, int in_dtype, cudaStream_t st);
 
+// Work of one GEMM launch: algorithmic flop (2 per multiply-add on the tiles and k-ranges
+// that the structure flags keep, unpadded) and issued flop (padded tiles x products).
+void gemm_work(const GemmDesc& d, int k_granule, double* algorithmic, double* issued, int products);
+
 // Copies the strict upper triangle of a square matrix onto its lower triangle.
 int mirror_upper_to_lower(float* H, int64_t C, int64_t ldh, cudaStream_t st);
 

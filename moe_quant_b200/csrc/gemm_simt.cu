@@ -4,6 +4,7 @@
 // (src/gptq.py:13-14, 103; src/gptq_loop.py:148).  128x128x8 tiles, 8x8 outputs
 // per thread, double-buffered shared memory.
 #include "gemm.cuh"
+#include "profile.cuh"
 
 namespace mq {
 
@@ -156,8 +157,39 @@ __global__ void __launch_bounds__(256) mirror_kernel(float* __restrict__ H, int6
 
 }  // namespace
 
+void gemm_work(const GemmDesc& d, int k_granule, double* algorithmic, double* issued, int products) {
+  double alg = 0.0, iss = 0.0;
+  for (int b = 0; b < d.batch; ++b) {
+    int N = d.N, K = d.K;
+    if (d.n_step) {
+      int left = d.n_total - b * d.n_step;
+      N = N < left ? N : left;
+      if (d.k_follows_n) K = N;
+    }
+    if (N <= 0) continue;
+    for (int m0 = 0; m0 < d.M; m0 += 128) {
+      for (int n0 = 0; n0 < N; n0 += 128) {
+        if (d.upper_tiles_only && n0 + 128 <= m0) continue;
+        int k_lo = d.a_upper ? m0 : 0;
+        int k_hi = K;
+        if (d.b_upper && n0 + 128 < k_hi) k_hi = n0 + 128;
+        if (k_hi <= k_lo) continue;
+        int rows = d.M - m0 < 128 ? d.M - m0 : 128, cols = N - n0 < 128 ? N - n0 : 128;
+        alg += 2.0 * rows * cols * (k_hi - k_lo);
+        int kp = (k_hi - k_lo + k_granule - 1) / k_granule * k_granule;
+        iss += 2.0 * 128 * 128 * kp * products;
+      }
+    }
+  }
+  *algorithmic = alg;
+  *issued = iss;
+}
+
 int gemm_simt(const GemmDesc& d, int in_dtype, cudaStream_t st) {
   if (d.M <= 0 || d.N <= 0 || d.batch <= 0) return MQ_OK;
+  double flop_alg = 0.0, flop_issued = 0.0;
+  if (g_profile_on) gemm_work(d, 8, &flop_alg, &flop_issued, 1);
+  ProfScope prof(PROF_SIMT_GEMM, flop_alg, flop_issued, st);
   switch (in_dtype) {
     case MQ_F32: return launch<float>(d, st);
     case MQ_BF16: return launch<__nv_bfloat16>(d, st);

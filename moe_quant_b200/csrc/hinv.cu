@@ -21,6 +21,7 @@
 // log2(C/128) levels of two batched GEMMs each.
 #include "gemm.cuh"
 #include "engine.cuh"
+#include "profile.cuh"
 
 namespace mq {
 
@@ -236,11 +237,17 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
     const int64_t k1 = (int64_t)p * NB;
     const int nb = (int)((C - k1) < NB ? (C - k1) : NB);
     float* dblk = H + k1 * ldh + k1;
-    chol_diag_rev_kernel<<<1, 256, 0, st>>>(dblk, ldh, nb, (int)k1, flags);
+    {
+      ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
+      chol_diag_rev_kernel<<<1, 256, 0, st>>>(dblk, ldh, nb, (int)k1, flags);
+    }
     MQ_LAUNCH_CHECK();
     if (k1 == 0) break;
     int grid = (int)(ceil_div(k1, 8) < 148 * 2 ? ceil_div(k1, 8) : 148 * 2);
-    trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0);
+    {
+      ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
+      trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0);
+    }
     MQ_LAUNCH_CHECK();
     GemmDesc g;
     g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;

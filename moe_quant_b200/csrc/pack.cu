@@ -6,6 +6,7 @@
 // (pack_quantized_model.py:57-75) and dequantize_linear_weight
 // (src/quant_utils.py:243-256).
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace mq {
 
@@ -106,6 +107,7 @@ extern "C" int mq_pack_int4(const uint8_t* codes, int64_t R, int64_t C, const in
                (long long)group, (long long)C);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ProfScope prof(PROF_PACK, 1.5 * (double)R * (double)C, 0.0, st);
   if (!zero_i8 && C % 16 == 0 && aligned(codes, 16) && aligned(packed, 8)) {
     int64_t n_vec = R * C / 16;
     pack_int4_vec16<<<grid_for(n_vec, kPackThreads), kPackThreads, 0, st>>>(

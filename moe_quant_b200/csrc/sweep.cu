@@ -15,6 +15,7 @@
 // is a GEMM through the Engine.  Codes are written straight into the (R, C) uint8
 // result, so the transposes of src/gptq.py:191-199 never happen.
 #include "engine.cuh"
+#include "profile.cuh"
 
 namespace mq {
 
@@ -128,6 +129,9 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   const size_t smem = TILE * TILE * sizeof(float);
   for (int64_t i1 = 0; i1 < C; i1 += TILE) {
     const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
+    // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
+    {
+    ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
     switch (out_dtype) {
       case MQ_F32:
         sweep_tile_kernel<MQ_F32><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
@@ -143,6 +147,7 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
         sweep_tile_kernel<MQ_F16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
                                                                   (int)i1, nb);
+    }
     }
     MQ_LAUNCH_CHECK();
     const int64_t i2 = i1 + nb;

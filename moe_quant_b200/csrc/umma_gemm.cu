@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include "engine.cuh"
+#include "profile.cuh"
 
 namespace mq {
 
@@ -385,6 +386,7 @@ int pad_to(int x, int a) { return (x + a - 1) / a * a; }
 template <typename TIn, typename TPlane>
 int launch_split(const SplitParams& sp, int batch, cudaStream_t st) {
   dim3 grid((unsigned)(sp.K_pad / 32), (unsigned)(sp.rows_pad / 32), (unsigned)batch);
+  ProfScope prof(PROF_SPLIT, (double)batch * sp.rows_pad * sp.K_pad * (sizeof(TIn) + 2.0 * sp.planes), 0.0, st);
   if (sp.rs == 1 && sp.cs != 1)
     split_planes_kernel<TIn, TPlane, true><<<grid, 256, 0, st>>>(sp);
   else
@@ -458,6 +460,9 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   dim3 grid((unsigned)ceil_div(d.N, TILE_N), (unsigned)ceil_div(d.M, TILE_M), (unsigned)d.batch);
+  double flop_alg = 0.0, flop_issued = 0.0;
+  if (g_profile_on) gemm_work(d, SLAB_K, &flop_alg, &flop_issued, p.nterms);
+  ProfScope prof(PROF_UMMA_GEMM, flop_alg, flop_issued, st);
   umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
   MQ_LAUNCH_CHECK();
   return MQ_OK;

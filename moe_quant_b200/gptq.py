@@ -67,8 +67,9 @@ class GPTQ:
         if tied_gptq_handle is not None:
             tied_gptq_handle.num_tied_handles += 1
         self.issue_zero_samples = False
-        self.issue_nan_hessian = False
-        self.issue_non_invertible = False
+        self._nan_hessian = False
+        self._non_invertible = False
+        self._pending_flags: List[Tensor] = []   # device-side status words not yet read back
         self.precision = precision
         self.pre_step_completed = False
         self._hessian_ready = False   # True once H has been masked and damped
@@ -78,6 +79,33 @@ class GPTQ:
     @staticmethod
     def _validate_layer(layer) -> None:
         assert isinstance(layer, (nn.Linear, _ConvNd)), "OBC supports only linear and convolutional layers."
+
+    # The NaN / non-invertible checks run on the device.  Their status words are read back
+    # only when one of these attributes is looked at, so quantize() itself never blocks the host.
+    def _resolve_flags(self) -> None:
+        for flags in self._pending_flags:
+            nan, _dead, _zero, not_pd = flags.tolist()
+            self._nan_hessian = self._nan_hessian or bool(nan)
+            self._non_invertible = self._non_invertible or bool(not_pd)
+        self._pending_flags = []
+
+    @property
+    def issue_nan_hessian(self) -> bool:
+        self._resolve_flags()
+        return self._nan_hessian
+
+    @issue_nan_hessian.setter
+    def issue_nan_hessian(self, value: bool) -> None:
+        self._nan_hessian = bool(value)
+
+    @property
+    def issue_non_invertible(self) -> bool:
+        self._resolve_flags()
+        return self._non_invertible
+
+    @issue_non_invertible.setter
+    def issue_non_invertible(self, value: bool) -> None:
+        self._non_invertible = bool(value)
 
     def has_hessian_issues(self) -> bool:
         return any([self.issue_zero_samples, self.issue_nan_hessian, self.issue_non_invertible])
@@ -171,9 +199,7 @@ class GPTQ:
         return w.flatten(1, -1) if w.dim() > 2 else w
 
     def _absorb_flags(self, flags: Tensor) -> None:
-        nan, _dead, _zero, not_pd = flags.tolist()   # the one host sync of a layer
-        self.issue_nan_hessian = self.issue_nan_hessian or bool(nan)
-        self.issue_non_invertible = self.issue_non_invertible or bool(not_pd)
+        self._pending_flags.append(flags)
 
     @torch.no_grad()
     def _quantize(self, bits: int) -> Tuple[Tensor, Tensor, Tensor]:
@@ -290,8 +316,8 @@ def quantize_tied(handles: Sequence[GPTQ], bits: int) -> List[Tuple[Tensor, Tens
     out = []
     for h, q, s in zip(handles, codes, scales):
         h._hessian_ready = True
-        h.issue_nan_hessian = owner.issue_nan_hessian
-        h.issue_non_invertible = owner.issue_non_invertible
+        if h is not owner:
+            h._absorb_flags(flags)
         s = s.to(h.W_dtype)
         z = torch.full_like(s, (2 ** int(bits)) / 2)
         if h.is_distributed and dist_utils.is_dist_available_and_initialized():

@@ -108,6 +108,23 @@ int mq_hessian_prepare(float* H, int64_t C, int64_t ldh, float* W, int64_t R, in
                        void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_hessian_prepare_workspace_bytes(int64_t C);
 
+/* ------------------------------------------------------------------ no counterpart in the reference
+ * mq_hessian_prepare for callers that cannot supply scratch memory: a C host that only holds
+ * the H and W pointers, a plug-in that must not call the allocator of the process it runs in,
+ * or a path on which cudaMalloc (which synchronises the device) is off limits.  Same arguments
+ * and results as mq_hessian_prepare minus the workspace; the channel lists live in a
+ * static device array inside the library instead.
+ *   - limit: C <= 32768 input channels (the array is about 256 KB per GPU, held until the
+ *     process exits); larger C returns MQ_ERR_UNSUPPORTED and changes nothing;
+ *   - the library makes no allocation and frees nothing in this call;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls on a device share the one array, which keeps what the previous call left
+ *     (each call clears what it needs): two calls that overlap on the GPU, e.g. on two
+ *     streams, race.  Serialise them.  */
+int mq_hessian_prepare_noalloc(float* H, int64_t C, int64_t ldh, float* W, int64_t R, int64_t ldw,
+                               float rel_damp, mq_layer_flags* flags, void* stream);
+
 /* ------------------------------------------------------------------ a5 (second half)
  * Uhat <- rownormalise(chol_upper(H^-1)):  upper triangular, unit diagonal, zeros below.
  * Replaces inv_sym + torch.linalg.cholesky(upper=True) + div_ by the diagonal

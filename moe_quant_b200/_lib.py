@@ -35,6 +35,8 @@ SIGNATURES = {
     "mq_hessian_prepare": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_float, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
     "mq_hessian_prepare_workspace_bytes": (c_size_t, [c_int64]),
+    "mq_hessian_prepare_noalloc": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_float, c_void_p,
+                                           c_void_p]),
     "mq_hinv_upper": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p,
                               c_void_p, c_size_t, c_void_p]),
     "mq_hinv_upper_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),

@@ -252,3 +252,45 @@ extern "C" int mq_absmax_scales(const float* W, int64_t R, int64_t C, int64_t ld
   MQ_LAUNCH_CHECK();
   return MQ_OK;
 }
+
+// ---------------------------------------------------------------------------- no-allocation variant
+// Some hosts of this library have no way to hand over scratch memory: a plain C program that
+// was given nothing but the H and W pointers by another runtime, a plug-in running inside a
+// process whose allocator it must not call (all device memory already belongs to a pool it
+// does not control), or code on a path where cudaMalloc's implicit device synchronisation is
+// not acceptable.  For them the channel lists of the preparation step live in this
+// file-scope array instead of a caller workspace.  It is sized for kNoAllocMaxChannels
+// input channels (about 256 KB) and every GPU that loads the library carries it until the
+// process exits.
+namespace mq {
+constexpr int64_t kNoAllocMaxChannels = 32768;
+constexpr size_t kNoAllocScratchBytes = ((kNoAllocMaxChannels * 4 + 255) / 256) * 256 + (((kNoAllocMaxChannels + 1) * 4 + 255) / 256) * 256;
+static __device__ __align__(256) unsigned char g_prepare_scratch[kNoAllocScratchBytes];
+}  // namespace mq
+
+extern "C" int mq_hessian_prepare_noalloc(float* H, int64_t C, int64_t ldh, float* W, int64_t R, int64_t ldw,
+                                          float rel_damp, mq_layer_flags* flags, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(C > 0, MQ_ERR_ARGUMENT, "mq_hessian_prepare_noalloc: bad C=%lld", (long long)C);
+  MQ_REQUIRE(C <= kNoAllocMaxChannels, MQ_ERR_UNSUPPORTED,
+             "mq_hessian_prepare_noalloc: C=%lld is beyond the built-in scratch (%lld channels); "
+             "use mq_hessian_prepare with a caller-provided workspace",
+             (long long)C, (long long)kNoAllocMaxChannels);
+  MQ_REQUIRE(mq_hessian_prepare_workspace_bytes(C) <= kNoAllocScratchBytes, MQ_ERR_UNSUPPORTED,
+             "mq_hessian_prepare_noalloc: built-in scratch too small for C=%lld", (long long)C);
+  // In host code the array's name is only a handle; the kernels need its device address,
+  // which differs per GPU.  Looked up once per device, with that device current.
+  static void* device_address[64] = {};
+  int dev = -1;
+  MQ_CUDA(cudaGetDevice(&dev));
+  MQ_REQUIRE(dev >= 0 && dev < 64, MQ_ERR_UNSUPPORTED, "mq_hessian_prepare_noalloc: device ordinal %d not supported", dev);
+  if (device_address[dev] == nullptr) {
+    void* p = nullptr;
+    MQ_CUDA(cudaGetSymbolAddress(&p, g_prepare_scratch));
+    MQ_REQUIRE(p != nullptr, MQ_ERR_CUDA, "mq_hessian_prepare_noalloc: no device address for the built-in scratch");
+    device_address[dev] = p;
+  }
+  // Same kernels, same order as mq_hessian_prepare; the zero-initialised parts of the scratch
+  // (column flags, list length) are cleared by that sequence on every call.
+  return mq_hessian_prepare(H, C, ldh, W, R, ldw, rel_damp, flags, device_address[dev], kNoAllocScratchBytes, stream);
+}

@@ -88,6 +88,19 @@ def hessian_prepare(H: Tensor, W: Optional[Tensor], rel_damp: float) -> Tensor:
     return flags
 
 
+def hessian_prepare_noalloc(H: Tensor, W: Optional[Tensor], rel_damp: float, flags: Tensor) -> None:
+    """hessian_prepare for hosts that cannot provide scratch: the channel lists live in a static
+    array inside the library (C <= 32768).  Even the 16-byte flag word is the caller's (`flags`,
+    int32[4] on H's device), so this call allocates nothing at all.  Calls on one device must
+    not overlap on the GPU: they share the array."""
+    require_cuda(H, "H")
+    require_cuda(flags, "flags")
+    with torch.cuda.device(H.device):
+        check(lib().mq_hessian_prepare_noalloc(ptr(H), H.shape[0], H.stride(0), ptr(W), 0 if W is None else W.shape[0],
+                                               0 if W is None else W.stride(0), rel_damp, ptr(flags),
+                                               stream_ptr(H.device)))
+
+
 def hinv_upper(H: Tensor, precision: Optional[Precision] = None, flags: Optional[Tensor] = None,
                want_diag: bool = False) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
     """Row-normalised upper Cholesky factor of H^-1.  H (damped) is DESTROYED.

@@ -30,12 +30,18 @@ namespace {
 constexpr int NB = 128;  // panel width
 
 // ------------------------------------------------------------------ diagonal block
-// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads, thread
-// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers.
+// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
+// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers.  The 128 pivots are
+// taken 8 at a time: the thread that owns diagonal tile kt factors it alone in registers
+// (no barrier inside), the 8-wide panel above it is solved by the threads of tile column
+// kt, and every remaining upper tile takes one rank-8 update.  Three barriers per 8 pivots.
+constexpr int PAN_LD = NB + 4;
+
 __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                             int k_global, mq_layer_flags* flags) {
-  __shared__ float colv[NB];
-  __shared__ float piv;
+  __shared__ __align__(16) float pan[8][PAN_LD];  // pan[kk][row]: column 8kt+kk of T, rows above the leaf
+  __shared__ float leaf[8][8];                    // leaf[j][kk] = T[8kt+j][8kt+kk]
+  __shared__ float rdiag[8];                      // 1 / T[8kt+kk][8kt+kk]
   const int t = threadIdx.x;
   const int tr = t >> 4, tc = t & 15;
   float a[8][8];
@@ -47,48 +53,67 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
       a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
     }
   for (int kt = 15; kt >= 0; --kt) {
+    if (tr == kt && tc == kt) {
 #pragma unroll
-    for (int kk = 7; kk >= 0; --kk) {
-      const int k = kt * 8 + kk;
-      if (tr == kt && tc == kt) piv = a[kk][kk];
-      __syncthreads();
-      float d = piv;
-      if (!(d > 0.0f)) {  // also catches NaN
-        if (t == 0 && k < nb) atomicCAS(&flags->not_positive, 0, k_global + k + 1);
-        d = 1.0f;
+      for (int kk = 7; kk >= 0; --kk) {
+        float d = a[kk][kk];
+        if (!(d > 0.0f)) {  // also catches NaN
+          if (kt * 8 + kk < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + kk + 1);
+          d = 1.0f;
+        }
+        float r = rsqrtf(d);
+        r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
+        a[kk][kk] = d * r;
+        rdiag[kk] = r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < kk) a[i][kk] *= r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (i <= j && j < kk) a[i][j] = fmaf(-a[i][kk], a[j][kk], a[i][j]);
       }
-      const float tkk = sqrtf(d);
-      if (tc == kt && tr <= kt) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) leaf[j][kk] = (j < kk) ? a[j][kk] : 0.0f;
+    }
+    __syncthreads();
+    if (tc == kt && tr < kt) {
+      // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
+#pragma unroll
+      for (int kk = 7; kk >= 0; --kk) {
+        const float rd = rdiag[kk];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          int row = tr * 8 + i;
-          if (row < k) {
-            a[i][kk] = a[i][kk] / tkk;
-            colv[row] = a[i][kk];
-          }
+          const float pv = a[i][kk] * rd;
+          a[i][kk] = pv;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j < kk) a[i][j] = fmaf(-pv, leaf[j][kk], a[i][j]);
         }
-        if (tr == kt) a[kk][kk] = tkk;
       }
-      __syncthreads();
-      if (tr <= tc && tc <= kt) {
-        float ci[8], cj[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          ci[i] = colv[tr * 8 + i];
-          cj[i] = colv[tc * 8 + i];
-        }
-        if (tc < kt) {
+      for (int kk = 0; kk < 8; ++kk) {
+        *reinterpret_cast<float4*>(&pan[kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
+        *reinterpret_cast<float4*>(&pan[kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
+      }
+    }
+    __syncthreads();
+    if (tr <= tc && tc < kt) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
+      for (int kk = 0; kk < 8; ++kk) {
+        const float4 i0 = *reinterpret_cast<const float4*>(&pan[kk][tr * 8]);
+        const float4 i1 = *reinterpret_cast<const float4*>(&pan[kk][tr * 8 + 4]);
+        const float4 j0 = *reinterpret_cast<const float4*>(&pan[kk][tc * 8]);
+        const float4 j1 = *reinterpret_cast<const float4*>(&pan[kk][tc * 8 + 4]);
+        const float pi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+        const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-ci[i], cj[j], a[i][j]);
-        } else {
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j < kk) a[i][j] = fmaf(-ci[i], cj[j], a[i][j]);
-        }
+          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-pi[i], pj[j], a[i][j]);
       }
     }
   }
@@ -116,7 +141,8 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
                                                         int nrows, int nb_full, int n_total) {
   extern __shared__ __align__(16) float smem[];
   float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
-  float* dg = smem + NB * TT_LD;   // [NB]
+  float* dg = smem + NB * TT_LD;   // [NB] diagonal of T
+  float* rdg = dg + NB;            // [NB] its reciprocal
   const int b = blockIdx.y;
   int nb = nb_full;
   if (n_total > 0) {  // batched over diagonal blocks: the last one may be narrower
@@ -126,48 +152,87 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
   }
   tblk += (int64_t)b * t_bs;
   rows += (int64_t)b * r_bs;
-  for (int idx = threadIdx.x; idx < NB * NB; idx += blockDim.x) {
-    int j = idx >> 7, k = idx & 127;  // element T[j][k], coalesced over k
-    float v = (j < nb && k < nb) ? tblk[(int64_t)j * ldt + k] : (j == k ? 1.0f : 0.0f);
-    TT[k * TT_LD + j] = (j < k) ? v : 0.0f;
-    if (j == k) dg[k] = v;
+  {
+    // 16 independent float4 loads per thread are issued before any is used (one memory
+    // latency for the whole 64 KB block instead of one per element)
+    float4 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = threadIdx.x + i * 256;     // float4 index: row j, columns k4..k4+3
+      const int j = idx >> 5, k4 = (idx & 31) * 4;
+      v[i] = (j < nb && k4 < nb) ? __ldg(reinterpret_cast<const float4*>(tblk + (int64_t)j * ldt + k4))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      const int j = idx >> 5, k4 = (idx & 31) * 4;
+      const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = k4 + q;
+        const float val = (j < nb && k < nb) ? e[q] : (j == k ? 1.0f : 0.0f);
+        TT[k * TT_LD + j] = (j < k) ? val : 0.0f;
+        if (j == k) {
+          dg[k] = val;
+          rdg[k] = 1.0f / val;
+        }
+      }
+    }
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
-  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < nrows; r += gridDim.x * warps_per_block) {
-    float a[4];
-    float* rp = rows + (int64_t)r * ldr;
-    if (IDENTITY) {
+  // Two rows per warp at a time: their substitution chains are independent, so one hides the
+  // shuffle and FMA latency of the other.
+  for (int r0 = 2 * (blockIdx.x * warps_per_block + (threadIdx.x >> 5)); r0 < nrows; r0 += 2 * gridDim.x * warps_per_block) {
+    float a[2][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) a[q] = (lane * 4 + q == r) ? 1.0f : 0.0f;
-    } else if (lane * 4 < nb) {
-      float4 v = *reinterpret_cast<const float4*>(rp + lane * 4);
-      a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
-    } else {
-      a[0] = a[1] = a[2] = a[3] = 0.0f;
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + h;
+      if (IDENTITY) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) a[h][q] = (lane * 4 + q == r) ? 1.0f : 0.0f;
+      } else if (r < nrows && lane * 4 < nb) {
+        float4 v = *reinterpret_cast<const float4*>(rows + (int64_t)r * ldr + lane * 4);
+        a[h][0] = v.x; a[h][1] = v.y; a[h][2] = v.z; a[h][3] = v.w;
+      } else {
+        a[h][0] = a[h][1] = a[h][2] = a[h][3] = 0.0f;
+      }
     }
     for (int kq = (nb >> 2) - 1; kq >= 0; --kq) {
 #pragma unroll
       for (int kk = 3; kk >= 0; --kk) {
         const int k = kq * 4 + kk;
-        float p = a[kk] / dg[k];
-        p = __shfl_sync(0xffffffffu, p, kq);
+        const float d = dg[k], rd = rdg[k];
         const float4 tt = *reinterpret_cast<const float4*>(&TT[k * TT_LD + lane * 4]);
-        a[0] = fmaf(-p, tt.x, a[0]);
-        a[1] = fmaf(-p, tt.y, a[1]);
-        a[2] = fmaf(-p, tt.z, a[2]);
-        a[3] = fmaf(-p, tt.w, a[3]);
-        if (lane == kq) a[kk] = p;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          // a / d through the reciprocal and one correction step (the quotient refinement of a
+          // correctly rounded division), a few FMAs instead of the full division sequence
+          float p = a[h][kk] * rd;
+          p = fmaf(fmaf(-d, p, a[h][kk]), rd, p);
+          p = __shfl_sync(0xffffffffu, p, kq);
+          a[h][0] = fmaf(-p, tt.x, a[h][0]);
+          a[h][1] = fmaf(-p, tt.y, a[h][1]);
+          a[h][2] = fmaf(-p, tt.z, a[h][2]);
+          a[h][3] = fmaf(-p, tt.w, a[h][3]);
+          if (lane == kq) a[h][kk] = p;
+        }
       }
     }
     if (lane * 4 < nb) {
-      if (IDENTITY) {
-        // result row r is column r of T^-1
 #pragma unroll
-        for (int q = 0; q < 4; ++q) rows[(int64_t)(lane * 4 + q) * ldr + r] = a[q];
-      } else {
-        *reinterpret_cast<float4*>(rp + lane * 4) = make_float4(a[0], a[1], a[2], a[3]);
+      for (int h = 0; h < 2; ++h) {
+        const int r = r0 + h;
+        if (r >= nrows) continue;
+        if (IDENTITY) {
+          // result row r is column r of T^-1
+#pragma unroll
+          for (int q = 0; q < 4; ++q) rows[(int64_t)(lane * 4 + q) * ldr + r] = a[h][q];
+        } else {
+          *reinterpret_cast<float4*>(rows + (int64_t)r * ldr + lane * 4) = make_float4(a[h][0], a[h][1], a[h][2], a[h][3]);
+        }
       }
     }
   }
@@ -200,7 +265,7 @@ __global__ void __launch_bounds__(256) identity_if_failed_kernel(float* __restri
   }
 }
 
-constexpr size_t kTrsmSmem = (size_t)(NB * TT_LD + NB) * sizeof(float);
+constexpr size_t kTrsmSmem = (size_t)(NB * TT_LD + 2 * NB) * sizeof(float);
 
 int configure_once() {
   static bool done[64] = {};
@@ -243,7 +308,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
     }
     MQ_LAUNCH_CHECK();
     if (k1 == 0) break;
-    int grid = (int)(ceil_div(k1, 8) < 148 * 2 ? ceil_div(k1, 8) : 148 * 2);
+    int grid = (int)(ceil_div(k1, 16) < 148 * 2 ? ceil_div(k1, 16) : 148 * 2);
     {
       ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
       trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0);
@@ -265,7 +330,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
   MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
-  trsm_rows_kernel<true><<<dim3(16, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
+  trsm_rows_kernel<true><<<dim3(8, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
                                                              (int64_t)NB * (ldu + 1), NB, NB, (int)C);
   MQ_LAUNCH_CHECK();
   for (int64_t s = NB; s < C; s *= 2) {

@@ -56,7 +56,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: gives up after about two seconds and records `code`.
+// Bounded wait: gives up after about one second and records `code`.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
@@ -70,10 +70,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
         : "memory");
     if (ok) return true;
     if ((it & 255u) == 255u) {
+      // once any wait on this device has expired, every later wait gives up at once
+      if (*reinterpret_cast<volatile int*>(&g_engine_fault) != 0) return false;
       uint64_t now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 2000000000ull) {
+      else if (now - t0 > 1000000000ull) {
         atomicCAS(&g_engine_fault, 0, code);
         return false;
       }
@@ -269,6 +271,185 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
   }
 }
 
+// ---------------------------------------------------------------- K <= 128: A-stationary panel GEMM
+// The factorisation's trailing updates and the sweep's lazy updates are rank-128 updates of
+// a large fp32 matrix: K is one or two slabs, the output is what moves.  One CTA takes one
+// 128-row block of A, keeps all of its planes in shared memory, and walks a run of n-tiles:
+//   warp 0 : TMA, A once, then the B tiles of successive n-tiles through a 2-stage ring
+//   warp 1 : tcgen05.mma into two alternating 128-column TMEM accumulators
+//   warps 2..5 : epilogue of tile i (TMEM -> registers -> C += ...) while tile i+1 is multiplied
+// so the read-modify-write of C, the B loads and the tensor pipe overlap.
+constexpr int PANEL_MAX_RUN = 16;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_b,
+                                                                  const UmmaParams p, const int run) {
+  const int m0 = blockIdx.y * TILE_M;
+  const int n_tiles = (p.N + TILE_N - 1) / TILE_N;
+  const int first = p.upper_tiles_only ? (int)blockIdx.y : 0;
+  const int nt_begin = first + (int)blockIdx.x * run;
+  int nt_end = nt_begin + run;
+  if (nt_end > n_tiles) nt_end = n_tiles;
+  if (nt_begin >= nt_end || m0 >= p.M) return;
+  const int n_slabs = (p.K + SLAB_K - 1) / SLAB_K;  // 1 or 2
+  const int count = nt_end - nt_begin;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_bytes = (uint32_t)(n_slabs * p.planes) * PLANE_TILE_BYTES;
+  const uint32_t b_stage_bytes = (uint32_t)p.planes * PLANE_TILE_BYTES;
+  const uint32_t b_base = smem_base + 2u * (uint32_t)p.planes * PLANE_TILE_BYTES;  // A always reserves two slabs
+  __shared__ __align__(8) uint64_t bars[9];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t a_full = smem_u32(&bars[0]);
+  const uint32_t b_full = smem_u32(&bars[1]), b_empty = smem_u32(&bars[3]);
+  const uint32_t acc_full = smem_u32(&bars[5]), acc_empty = smem_u32(&bars[7]);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(a_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(b_empty + 8 * s, 1);
+      mbar_init(acc_full + 8 * s, 1);
+      mbar_init(acc_empty + 8 * s, 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 2 * TILE_N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(a_full, a_bytes);
+      for (int s = 0; s < n_slabs; ++s)
+        for (int pl = 0; pl < p.planes; ++pl)
+          tma_load_3d(smem_base + (uint32_t)(s * p.planes + pl) * PLANE_TILE_BYTES, &map_a, a_full, s * SLAB_K, m0, pl);
+      int it = 0;
+      bool ok = true;
+      for (int i = 0; i < count && ok; ++i) {
+        const int b_row = (nt_begin + i) * TILE_N;
+        for (int s = 0; s < n_slabs; ++s, ++it) {
+          const int st = it & 1;
+          if (it >= 2 && !mbar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1, 11)) { ok = false; break; }
+          mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
+          for (int pl = 0; pl < p.planes; ++pl)
+            tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
+                        s * SLAB_K, b_row, pl);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(a_full, 0, 12);
+      int it = 0;
+      for (int i = 0; i < count && ok; ++i) {
+        const int acc = i & 1;
+        if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 13);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t accumulate = 0;
+        for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+          const int st = it & 1;
+          ok = mbar_wait(b_full + 8 * st, (it >> 1) & 1, 14);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_tile = smem_base + (uint32_t)(s * p.planes) * PLANE_TILE_BYTES;
+          const uint32_t b_tile = b_base + (uint32_t)st * b_stage_bytes;
+#pragma unroll
+          for (int kk = 0; kk < SLAB_K / 16; ++kk) {
+            for (int t = 0; t < p.nterms; ++t) {
+              const uint64_t ad = kmajor_sw128_desc(a_tile + p.term_a[t] * PLANE_TILE_BYTES + kk * 32);
+              const uint64_t bd = kmajor_sw128_desc(b_tile + p.term_b[t] * PLANE_TILE_BYTES + kk * 32);
+              umma_bf16(tmem_acc + (uint32_t)(acc * TILE_N), ad, bd, p.idesc, accumulate);
+              accumulate = 1;
+            }
+          }
+          umma_commit(b_empty + 8 * st);
+        }
+        umma_commit(acc_full + 8 * acc);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    float* __restrict__ C = p.C;
+    const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    bool ok = true;
+    for (int i = 0; i < count && ok; ++i) {
+      const int acc = i & 1;
+      const int n0 = (nt_begin + i) * TILE_N;
+      float* dst_row = C + (int64_t)row * p.ldc + n0;
+      // tcgen05.ld is a warp-wide instruction: the choice of path must be uniform in the warp
+      const bool whole = __all_sync(0xffffffffu, vec_ok && row < p.M && n0 + TILE_N <= p.N);
+      if (whole) {
+        // All 128 values of this thread's row are requested before the accumulator is waited
+        // for, so the DRAM/L2 latency of C overlaps the MMAs of this tile.
+        float4 old[TILE_N / 4];
+        if (p.beta != 0.0f) {
+#pragma unroll
+          for (int j = 0; j < TILE_N / 4; ++j) old[j] = *reinterpret_cast<const float4*>(dst_row + 4 * j);
+        }
+        ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o = make_float4(p.alpha * v[4 * j], p.alpha * v[4 * j + 1], p.alpha * v[4 * j + 2], p.alpha * v[4 * j + 3]);
+            if (p.beta != 0.0f) {
+              const float4 od = old[c * 8 + j];
+              o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
+              o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
+            }
+            *reinterpret_cast<float4*>(dst_row + c * 32 + 4 * j) = o;
+          }
+        }
+      } else {
+        ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          float v[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+          if (row < p.M && col0 < p.N) {
+            float* dst = dst_row + c * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.N) {
+                float o = p.alpha * v[j];
+                if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
+                dst[j] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, 2 * TILE_N);
+  }
+}
+
 // ---------------------------------------------------------------- operand planes
 // dst plane pl, batch b, row r, k  <-  piece pl of src[b][r][k]; zero outside the logical
 // (rows_b x K_b) extent up to the padded (rows_pad x K_pad) one.  32 x 32 tiles; when the
@@ -426,6 +607,7 @@ int configure_once() {
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -463,7 +645,20 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   double flop_alg = 0.0, flop_issued = 0.0;
   if (g_profile_on) gemm_work(d, SLAB_K, &flop_alg, &flop_issued, p.nterms);
   ProfScope prof(PROF_UMMA_GEMM, flop_alg, flop_issued, st);
-  umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
+  if (d.K <= 2 * SLAB_K && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.K > 0) {
+    // rank-<=128 update: keep A in shared memory and walk runs of n-tiles
+    const int m_tiles = (int)ceil_div(d.M, TILE_M), n_tiles = (int)ceil_div(d.N, TILE_N);
+    const long long tiles = d.upper_tiles_only ? (long long)n_tiles * (n_tiles + 1) / 2 : (long long)m_tiles * n_tiles;
+    // about one CTA per SM, each walking a long run, so the fixed cost of a CTA (barriers, TMEM,
+    // first operand load) is paid once per SM instead of once per tile
+    int run = (int)((tiles + 147) / 148);
+    run = run < 1 ? 1 : (run > PANEL_MAX_RUN ? PANEL_MAX_RUN : run);
+    dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);
+    const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024;  // A: two slabs, B: two stages
+    umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, p, run);
+  } else {
+    umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
+  }
   MQ_LAUNCH_CHECK();
   return MQ_OK;
 }

@@ -95,6 +95,19 @@ int mq_hessian_accum(const void* X, int x_dtype, int64_t m, int64_t C, int64_t l
                      int math, int split, void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_hessian_accum_workspace_bytes(int x_dtype, int64_t m, int64_t C, int math, int split);
 
+/* ------------------------------------------------------------------ the contraction engine by itself
+ * C[m,n] = alpha * sum_k A[m,k] B[k,n] + beta * C[m,n] on fp32 operands with arbitrary element
+ * strides (A[m,k] at A[m*a_rs + k*a_cs], B[k,n] at B[k*b_rs + n*b_cs]), C row-major.
+ * This is the GEMM that stands in for every torch addmm_ on the path (src/gptq.py:103,
+ * src/gptq_loop.py:148) and for the library factorisations' inner products; it is exported so
+ * that it can be tested and timed alone.  upper_tiles_only skips 128x128 output tiles that lie
+ * entirely below the diagonal.  */
+int mq_gemm(const float* A, int64_t a_rs, int64_t a_cs, const float* B, int64_t b_rs, int64_t b_cs,
+            float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+            int upper_tiles_only, int math, int split,
+            void* workspace, size_t workspace_bytes, void* stream);
+size_t mq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split);
+
 /* ------------------------------------------------------------------ a3 + a5 (first half)
  * In place on H (C,C) and on the fp32 working copy W (R,C):
  *   NaN anywhere in H -> H = I;  diag(H)==0 -> 1 and that W column -> 0
@@ -138,6 +151,15 @@ int mq_hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, fl
                   void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_hinv_upper_workspace_bytes(int64_t C, int math, int split);
 
+/* The first half of mq_hinv_upper alone: H (damped) -> Utilde = T diag(T)^-1 in place (unit upper
+ * triangular, zeros below), with H = T T^T; diag_out (optional, C floats) receives diag(T).
+ * Utilde is the inverse of Uhat.  mq_gptq_sweep accepts it directly (W_original != NULL), which
+ * saves the triangular inverse: that is what mq_quantize_layer does.  Non-positive pivot:
+ * flags->not_positive is set and the result is I.
+ * workspace: mq_gemm_workspace_bytes(C, C, 128, math, split) + 256 + 4*C bytes.  */
+int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag_out, int math, int split,
+                        mq_layer_flags* flags, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------ a4
  * scale[r, j] = round_to(out_dtype, (2/maxq) * max|W[r, j*g:(j+1)*g]| + 1e-12), kept as fp32.
  * Symmetric grid of find_quantization_meta / get_quantization_grid
@@ -155,13 +177,17 @@ int mq_absmax_scales(const float* W, int64_t R, int64_t C, int64_t ldw, int64_t 
  *   dequantized : optional (R,C) out of out_dtype holding round_to(out_dtype,(q-zero)*scale).
  *   out_dtype   : the layer dtype that dequantized values are rounded through inside the
  *                 sweep (src/quant_utils.py:37-49).
+ *   W_original  : NULL for the reference's recurrence (Uhat given).  Otherwise a second, untouched
+ *                 fp32 copy of the weights (ldwo) and `Uhat` must hold the unit factor Utilde of
+ *                 mq_chol_unit_factor: the sweep then propagates -(y - w_original) against Utilde,
+ *                 which yields the same running weights without ever inverting the factor.
  * workspace: mq_gptq_sweep_workspace_bytes(R, C, math, split).  */
 int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw,
                   const float* Uhat, int64_t ldu,
                   const float* scale, const float* zero, int64_t group,
                   int64_t row_stride, int64_t group_stride,
                   int bits, int out_dtype,
-                  uint8_t* codes, void* dequantized,
+                  uint8_t* codes, void* dequantized, const float* W_original, int64_t ldwo,
                   int math, int split, void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
 

@@ -32,6 +32,9 @@ SIGNATURES = {
     "mq_hessian_accum": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float, c_float,
                                  c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "mq_hessian_accum_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int, c_int]),
+    "mq_gemm": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                        c_int64, c_float, c_float, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "mq_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_int]),
     "mq_hessian_prepare": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_float, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
     "mq_hessian_prepare_workspace_bytes": (c_size_t, [c_int64]),
@@ -42,8 +45,10 @@ SIGNATURES = {
     "mq_hinv_upper_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "mq_absmax_scales": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "mq_gptq_sweep": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
-                              c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t,
-                              c_void_p]),
+                              c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                              c_void_p, c_size_t, c_void_p]),
+    "mq_chol_unit_factor": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t,
+                                    c_void_p]),
     "mq_gptq_sweep_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
     "mq_quantize_layer": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,

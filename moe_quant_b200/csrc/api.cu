@@ -25,7 +25,9 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
-               void* deq, int math, int split, Workspace& ws, cudaStream_t st);
+               void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st);
+int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
+                     Workspace& ws, cudaStream_t st);
 int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
                          float alpha, int split, Workspace& ws, cudaStream_t st);
 size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, int split);
@@ -66,12 +68,38 @@ extern "C" int mq_hessian_accum(const void* X, int x_dtype, int64_t m, int64_t C
   return mirror_upper_to_lower(H, C, ldh, st);
 }
 
+// ---------------------------------------------------------------------------- the GEMM engine by itself
+extern "C" size_t mq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split) {
+  return mq::engine_workspace_bytes(M, N, K, math, split);
+}
+
+extern "C" int mq_gemm(const float* A, int64_t a_rs, int64_t a_cs, const float* B, int64_t b_rs, int64_t b_cs, float* C,
+                       int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta, int upper_tiles_only,
+                       int math, int split, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(A && B && C, MQ_ERR_ARGUMENT, "mq_gemm: null pointer");
+  MQ_REQUIRE(M > 0 && N > 0 && K >= 0 && ldc >= N, MQ_ERR_ARGUMENT, "mq_gemm: bad shape M=%lld N=%lld K=%lld ldc=%lld",
+             (long long)M, (long long)N, (long long)K, (long long)ldc);
+  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_gemm: bad math %d", math);
+  GemmDesc g;
+  g.A = A; g.a_rs = a_rs; g.a_cs = a_cs;
+  g.B = B; g.b_rs = b_rs; g.b_cs = b_cs;
+  g.C = C; g.ldc = ldc;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.alpha = alpha; g.beta = beta;
+  g.upper_tiles_only = upper_tiles_only;
+  Workspace ws(workspace, workspace_bytes);
+  Engine eng(math, split, ws, static_cast<cudaStream_t>(stream));
+  return eng.gemm(g);
+}
+
 // ---------------------------------------------------------------------------- a3..a8
 namespace mq {
 static size_t layer_fixed_bytes(int n_tied, int64_t R, int64_t C) {
   size_t b = 0;
-  b += align_up((size_t)C * C * sizeof(float), 256);                    // Uhat
-  b += (size_t)n_tied * align_up((size_t)R * C * sizeof(float), 256);   // fp32 working copies
+  b += align_up((size_t)C * C * sizeof(float), 256);                        // unit factor of the damped Hessian
+  b += align_up((size_t)C * sizeof(float), 256);                            // its diagonal scaling
+  b += 2 * (size_t)n_tied * align_up((size_t)R * C * sizeof(float), 256);   // fp32 weights: original and running
   b += mq_hessian_prepare_workspace_bytes(C);
   return b;
 }
@@ -81,7 +109,7 @@ extern "C" size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64
                                                     int split_sweep) {
   using namespace mq;
   if (n_tied <= 0 || R <= 0 || C <= 0) return 0;
-  size_t a = align_up((size_t)C * C * sizeof(float), 256) + hinv_workspace_bytes(C, math, split_hinv);  // + Hessian copy
+  size_t a = engine_workspace_bytes(C, C, 128, math, split_hinv);   // factorisation: rank-128 updates
   size_t b = sweep_workspace_bytes(R, C, math, split_sweep);
   return layer_fixed_bytes(n_tied, R, C) + (a > b ? a : b);
 }
@@ -107,12 +135,17 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace ws(workspace, workspace_bytes);
-  float* Uhat = ws.take<float>((size_t)C * C);
+  float* U = ws.take<float>((size_t)C * C);
+  float* diag = ws.take<float>(C);
   float* Wf[8];
-  for (int i = 0; i < n_tied; ++i) Wf[i] = ws.take<float>((size_t)R * C);
+  float* Wo[8];
+  for (int i = 0; i < n_tied; ++i) {
+    Wf[i] = ws.take<float>((size_t)R * C);
+    Wo[i] = ws.take<float>((size_t)R * C);
+  }
   void* prep = ws.take<char>(mq_hessian_prepare_workspace_bytes(C));
-  MQ_REQUIRE(Uhat && Wf[n_tied - 1] && prep, MQ_ERR_WORKSPACE, "mq_quantize_layer: workspace of %zu bytes is too small",
-             workspace_bytes);
+  MQ_REQUIRE(U && diag && Wf[n_tied - 1] && Wo[n_tied - 1] && prep, MQ_ERR_WORKSPACE,
+             "mq_quantize_layer: workspace of %zu bytes is too small", workspace_bytes);
 
   // W.clone().float()                                           src/gptq.py:149
   for (int i = 0; i < n_tied; ++i) MQ_TRY(launch_to_fp32(Wsrc[i], w_dtype, Wf[i], R * C, st));
@@ -122,23 +155,21 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   MQ_TRY(mq_hessian_prepare(H, C, ldh, Wf[0], R, C, rel_damp, flags, prep, mq_hessian_prepare_workspace_bytes(C), st));
   // grid                                                        src/quant_utils.py:75-101
   for (int i = 0; i < n_tied; ++i) MQ_TRY(mq_absmax_scales(Wf[i], R, C, C, group, bits, w_dtype, scale_out[i], st));
-  // Uhat                                                        src/gptq.py:236-242
+  // Factor a copy (the caller's H keeps the damped Hessian, which the reference leaves in
+  // handle.H, quant.py:314-316).  Only the unit factor Utilde = T diag(T)^-1 of H = T T^T is
+  // built: the sweep below runs in its inverse-free form, so the triangular inverse that
+  // src/gptq.py:236-242 needs (and mq_hinv_upper provides) is never computed here.
+  MQ_CUDA(cudaMemcpy2DAsync(U, C * sizeof(float), H, ldh * sizeof(float), C * sizeof(float), C, cudaMemcpyDeviceToDevice, st));
   {
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
-    // hinv_upper destroys its input; the caller's H must keep the damped Hessian
-    // (the reference leaves it in handle.H, quant.py:314-316), so factor a copy held in
-    // the sweep's part of the workspace.
-    float* Hwork = sub.take<float>((size_t)C * C);
-    MQ_REQUIRE(Hwork, MQ_ERR_WORKSPACE, "mq_quantize_layer: workspace too small for the Hessian copy");
-    MQ_CUDA(cudaMemcpy2DAsync(Hwork, C * sizeof(float), H, ldh * sizeof(float), C * sizeof(float), C,
-                              cudaMemcpyDeviceToDevice, st));
-    MQ_TRY(hinv_upper(Hwork, C, C, Uhat, C, nullptr, math, split_hinv, flags, sub, st));
+    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st));
   }
   // sweep                                                       src/gptq_loop.py:141-148
   for (int i = 0; i < n_tied; ++i) {
+    MQ_CUDA(cudaMemcpyAsync(Wo[i], Wf[i], (size_t)R * C * sizeof(float), cudaMemcpyDeviceToDevice, st));
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
-    MQ_TRY(gptq_sweep(Wf[i], R, C, C, Uhat, C, scale_out[i], nullptr, group, C / group, 1, bits, w_dtype, codes[i],
-                      dequantized ? dequantized[i] : nullptr, math, split_sweep, sub, st));
+    MQ_TRY(gptq_sweep(Wf[i], R, C, C, U, C, scale_out[i], nullptr, group, C / group, 1, bits, w_dtype, codes[i],
+                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st));
   }
   return MQ_OK;
 }

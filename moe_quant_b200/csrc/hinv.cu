@@ -288,14 +288,13 @@ size_t hinv_workspace_bytes(int64_t C, int math, int split) {
   return bytes;
 }
 
-int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float* diag_out, int math, int split,
-               mq_layer_flags* flags, Workspace& ws, cudaStream_t st) {
+// H (damped, symmetric; upper triangle read) -> unit upper factor Utilde = T diag(T)^-1 in place,
+// zeros below the diagonal.  diag (C floats, device) receives diag(T).  On a non-positive pivot
+// flags->not_positive is set and the result is replaced by I.
+int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
+                     Workspace& ws, cudaStream_t st) {
   MQ_TRY(configure_once());
-  float* diag = ws.take<float>(C);
-  float* scratch = ws.take<float>((size_t)C * C);
-  MQ_REQUIRE(diag && scratch, MQ_ERR_WORKSPACE, "mq_hinv_upper: workspace too small");
   Engine eng(math, split, ws, st);
-
   const int P = (int)ceil_div(C, NB);
   // ---- factorisation, last panel first
   for (int p = P - 1; p >= 0; --p) {
@@ -323,12 +322,26 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
     g.upper_tiles_only = 1;
     MQ_TRY(eng.gemm(g));
   }
-  // ---- T -> unit-diagonal factor, then its inverse
+  // ---- T -> unit-diagonal factor
   extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
-  if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
+  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags);
+  MQ_LAUNCH_CHECK();
+  return MQ_OK;
+}
+
+int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float* diag_out, int math, int split,
+               mq_layer_flags* flags, Workspace& ws, cudaStream_t st) {
+  float* diag = ws.take<float>(C);
+  float* scratch = ws.take<float>((size_t)C * C);
+  MQ_REQUIRE(diag && scratch, MQ_ERR_WORKSPACE, "mq_hinv_upper: workspace too small");
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st));
+  if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  Engine eng(math, split, ws, st);
+  const int P = (int)ceil_div(C, NB);
+  // ---- inverse of the unit factor: invert the diagonal blocks, then merge pairs of blocks
   MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
   trsm_rows_kernel<true><<<dim3(8, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
                                                              (int64_t)NB * (ldu + 1), NB, NB, (int)C);
@@ -378,4 +391,21 @@ extern "C" int mq_hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int6
   MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_hinv_upper: bad math %d", math);
   Workspace ws(workspace, workspace_bytes);
   return hinv_upper(H, C, ldh, Uhat, ldu, diag_out, math, split, flags, ws, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag_out, int math, int split,
+                                   mq_layer_flags* flags, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(H && flags, MQ_ERR_ARGUMENT, "mq_chol_unit_factor: null pointer");
+  MQ_REQUIRE(C > 0 && ldh >= C, MQ_ERR_ARGUMENT, "mq_chol_unit_factor: bad C=%lld ldh=%lld", (long long)C, (long long)ldh);
+  MQ_REQUIRE(C % 8 == 0, MQ_ERR_UNSUPPORTED, "mq_chol_unit_factor: C=%lld must be a multiple of 8", (long long)C);
+  MQ_REQUIRE(ldh % 4 == 0 && aligned(H, 16), MQ_ERR_ALIGNMENT, "mq_chol_unit_factor: H must be 16-byte aligned, ldh %% 4 == 0");
+  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_chol_unit_factor: bad math %d", math);
+  Workspace ws(workspace, workspace_bytes);
+  float* diag = ws.take<float>(C);
+  MQ_REQUIRE(diag, MQ_ERR_WORKSPACE, "mq_chol_unit_factor: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st));
+  if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return MQ_OK;
 }

@@ -29,7 +29,8 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     const float* __restrict__ W, int64_t ldw, int R, const float* __restrict__ U, int64_t ldu,
     const float* __restrict__ scale, const float* __restrict__ zero, int64_t group, int64_t s_rs, int64_t s_gs,
     float maxq, float zero_default, uint8_t* __restrict__ codes, int64_t C,
-    typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb) {
+    typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb,
+    const float* __restrict__ Worig, int64_t ldwo) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
@@ -65,6 +66,16 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     }
   }
   float qv[4] = {0.f, 0.f, 0.f, 0.f}, yv[4] = {0.f, 0.f, 0.f, 0.f}, ev[4] = {0.f, 0.f, 0.f, 0.f};
+  // Inverse-free form (Worig != nullptr): U is the unit factor Utilde = Uhat^-1 and what is
+  // propagated is minus the total change of the column, -(y - w_original), instead of the
+  // error against the running value; x_j = w_j - sum_{i<j} (y_i - w_i) Utilde[i,j] is the same
+  // number as the reference's running weight (E Uhat = Y - W  <=>  E = (Y - W) Utilde).
+  const bool inverse_free = Worig != nullptr;
+  float wo[4] = {0.f, 0.f, 0.f, 0.f};
+  if (inverse_free && have) {
+    float4 v = *reinterpret_cast<const float4*>(Worig + (int64_t)r * ldwo + c0);
+    wo[0] = v.x; wo[1] = v.y; wo[2] = v.z; wo[3] = v.w;
+  }
 
   const int n_quads = nb >> 2;
   for (int jq = 0; jq < n_quads; ++jq) {
@@ -74,7 +85,7 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
       const float x = w[t];
       const float q = fminf(fmaxf(floorf((x / sc[t] + zr[t]) + 0.5f), 0.0f), maxq);
       const float y = round_through<DT>((q - zr[t]) * sc[t]);
-      const float e = y - x;
+      const float e = inverse_free ? (wo[t] - y) : (y - x);
       if (lane == jq) { qv[t] = q; yv[t] = y; ev[t] = e; }
       const float eb = __shfl_sync(0xffffffffu, e, jq);
       const float4 u = *reinterpret_cast<const float4*>(&ublk[(jq * 4 + t) * TILE + lane * 4]);
@@ -118,7 +129,7 @@ size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
 
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
-               void* deq, int math, int split, Workspace& ws, cudaStream_t st) {
+               void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st) {
   MQ_TRY(configure_once());
   float* err = ws.take<float>((size_t)R * TILE);
   MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
@@ -136,17 +147,17 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       case MQ_F32:
         sweep_tile_kernel<MQ_F32><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<float*>(deq), err,
-                                                                  (int)i1, nb);
+                                                                  (int)i1, nb, Worig, ldwo);
         break;
       case MQ_BF16:
         sweep_tile_kernel<MQ_BF16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                    maxq, zero_default, codes, C,
-                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb);
+                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo);
         break;
       default:
         sweep_tile_kernel<MQ_F16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
-                                                                  (int)i1, nb);
+                                                                  (int)i1, nb, Worig, ldwo);
     }
     }
     MQ_LAUNCH_CHECK();
@@ -173,8 +184,9 @@ extern "C" size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, 
 
 extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu,
                              const float* scale, const float* zero, int64_t group, int64_t row_stride,
-                             int64_t group_stride, int bits, int out_dtype, uint8_t* codes, void* dequantized, int math,
-                             int split, void* workspace, size_t workspace_bytes, void* stream) {
+                             int64_t group_stride, int bits, int out_dtype, uint8_t* codes, void* dequantized,
+                             const float* W_original, int64_t ldwo, int math, int split, void* workspace,
+                             size_t workspace_bytes, void* stream) {
   using namespace mq;
   MQ_REQUIRE(W && Uhat && scale && codes, MQ_ERR_ARGUMENT, "mq_gptq_sweep: null pointer");
   MQ_REQUIRE(R > 0 && C > 0 && ldw >= C && ldu >= C, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad shape R=%lld C=%lld ldw=%lld ldu=%lld",
@@ -188,6 +200,10 @@ extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const 
              "mq_gptq_sweep: W/Uhat need 16-byte alignment and leading dimensions that are multiples of 4");
   MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad math %d", math);
   Workspace ws(workspace, workspace_bytes);
+  if (W_original) {
+    MQ_REQUIRE(ldwo >= C && ldwo % 4 == 0 && aligned(W_original, 16) && W_original != W, MQ_ERR_ALIGNMENT,
+               "mq_gptq_sweep: W_original must be a separate 16-byte aligned matrix with ldwo %% 4 == 0");
+  }
   return gptq_sweep(W, R, C, ldw, Uhat, ldu, scale, zero, group, row_stride, group_stride, bits, out_dtype, codes,
-                    dequantized, math, split, ws, static_cast<cudaStream_t>(stream));
+                    dequantized, W_original, ldwo, math, split, ws, static_cast<cudaStream_t>(stream));
 }

@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded; a wait that expires records a code in g_engine_fault,
 // the kernel still frees its TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "engine.cuh"
 #include "profile.cuh"
@@ -43,8 +44,8 @@ struct UmmaParams {
   int n_total, n_step, k_follows_n;
   int a_rows_pad, b_rows_pad;  // rows each batch occupies in the stacked plane buffers
   int planes, nterms, stages;
-  unsigned char term_a[MAX_TERMS], term_b[MAX_TERMS];
   uint32_t idesc;
+  int debug;  // timing experiments only: 1 = epilogue touches no global memory, 2 = no MMA is issued, 4 = no B loads
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -136,6 +137,40 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// All MMAs of one 64-wide K slab: for each of the four K16 steps, the products A_i B_j with
+// i + j < PLANES.  The issuing thread must feed the tensor pipe one MMA every ~64 cycles, so
+// the loops are unrolled at compile time and a descriptor costs one 32-bit add: only the
+// address field (low word) changes between tiles, planes and K steps.
+template <int PLANES>
+__device__ __forceinline__ void issue_slab(uint32_t tmem_d, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+                                           uint32_t& accumulate) {
+  const uint64_t a0 = kmajor_sw128_desc(a_tile), b0 = kmajor_sw128_desc(b_tile);
+  const uint32_t hi = (uint32_t)(a0 >> 32);
+  const uint32_t a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;
+#pragma unroll
+  for (int kk = 0; kk < SLAB_K / 16; ++kk) {
+#pragma unroll
+    for (int ti = 0; ti < PLANES; ++ti) {
+#pragma unroll
+      for (int tj = 0; tj < PLANES; ++tj) {
+        if (ti + tj < PLANES) {
+          const uint64_t ad = ((uint64_t)hi << 32) | (uint64_t)(a_lo + (uint32_t)((ti * PLANE_TILE_BYTES + kk * 32) >> 4));
+          const uint64_t bd = ((uint64_t)hi << 32) | (uint64_t)(b_lo + (uint32_t)((tj * PLANE_TILE_BYTES + kk * 32) >> 4));
+          umma_bf16(tmem_d, ad, bd, idesc, accumulate);
+          accumulate = 1;
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void issue_slab_any(int planes, uint32_t tmem_d, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+                                               uint32_t& accumulate) {
+  if (planes == 3) issue_slab<3>(tmem_d, a_tile, b_tile, idesc, accumulate);
+  else if (planes == 2) issue_slab<2>(tmem_d, a_tile, b_tile, idesc, accumulate);
+  else issue_slab<1>(tmem_d, a_tile, b_tile, idesc, accumulate);
+}
+
 // ---------------------------------------------------------------- the GEMM kernel
 __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ CUtensorMap map_b,
@@ -163,6 +198,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]), acc_bar = smem_u32(&bars[8]);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int planes = p.planes;
+  const uint32_t idesc = p.idesc;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -203,15 +240,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
         tc_fence_after();
         const uint32_t a_base = smem_base + st * stage_bytes;
         const uint32_t b_base = a_base + p.planes * PLANE_TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < SLAB_K / 16; ++kk) {
-          for (int t = 0; t < p.nterms; ++t) {
-            const uint64_t ad = kmajor_sw128_desc(a_base + p.term_a[t] * PLANE_TILE_BYTES + kk * 32);
-            const uint64_t bd = kmajor_sw128_desc(b_base + p.term_b[t] * PLANE_TILE_BYTES + kk * 32);
-            umma_bf16(tmem_acc, ad, bd, p.idesc, accumulate);
-            accumulate = 1;
-          }
-        }
+        issue_slab_any(planes, tmem_acc, a_base, b_base, idesc, accumulate);
         umma_commit(empty0 + 8 * st);  // the stage is free once these MMAs have read it
       }
       umma_commit(acc_bar);  // arrives when every MMA issued above has completed
@@ -280,6 +309,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
 //   warps 2..5 : epilogue of tile i (TMEM -> registers -> C += ...) while tile i+1 is multiplied
 // so the read-modify-write of C, the B loads and the tensor pipe overlap.
 constexpr int PANEL_MAX_RUN = 16;
+constexpr int STAGE_LD = 36;                               // floats per row of an epilogue staging tile
+constexpr int STAGE_BYTES = 4 * 32 * STAGE_LD * 4;         // four epilogue warps
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -310,6 +341,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   const uint32_t acc_full = smem_u32(&bars[5]), acc_empty = smem_u32(&bars[7]);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int planes = p.planes, debug = p.debug;
+  const uint32_t idesc = p.idesc;
   if (threadIdx.x == 0) {
     mbar_init(a_full, 1);
     for (int s = 0; s < 2; ++s) {
@@ -326,94 +359,119 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem_acc = tmem_slot;
 
+  // Producer and MMA warps run their loops with all 32 lanes (every lane waits on the
+  // barriers); one lane issues the TMA / tcgen05 instructions.
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(a_full, a_bytes);
       for (int s = 0; s < n_slabs; ++s)
-        for (int pl = 0; pl < p.planes; ++pl)
-          tma_load_3d(smem_base + (uint32_t)(s * p.planes + pl) * PLANE_TILE_BYTES, &map_a, a_full, s * SLAB_K, m0, pl);
-      int it = 0;
-      bool ok = true;
-      for (int i = 0; i < count && ok; ++i) {
-        const int b_row = (nt_begin + i) * TILE_N;
-        for (int s = 0; s < n_slabs; ++s, ++it) {
-          const int st = it & 1;
-          if (it >= 2 && !mbar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1, 11)) { ok = false; break; }
-          mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
-          for (int pl = 0; pl < p.planes; ++pl)
-            tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
-                        s * SLAB_K, b_row, pl);
+        for (int pl = 0; pl < planes; ++pl)
+          tma_load_3d(smem_base + (uint32_t)(s * planes + pl) * PLANE_TILE_BYTES, &map_a, a_full, s * SLAB_K, m0, pl);
+    }
+    int it = 0;
+    bool ok = true;
+    for (int i = 0; i < count && ok; ++i) {
+      const int b_row = (nt_begin + i) * TILE_N;
+      for (int s = 0; s < n_slabs; ++s, ++it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1, 11)) { ok = false; break; }
+        if (lane == 0) {
+          if (debug & 4) {
+            mbar_arrive(b_full + 8 * st);
+          } else {
+            mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
+            for (int pl = 0; pl < planes; ++pl)
+              tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
+                          s * SLAB_K, b_row, pl);
+          }
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      bool ok = mbar_wait(a_full, 0, 12);
-      int it = 0;
-      for (int i = 0; i < count && ok; ++i) {
-        const int acc = i & 1;
-        if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 13);
+    bool ok = mbar_wait(a_full, 0, 12);
+    int it = 0;
+    for (int i = 0; i < count && ok; ++i) {
+      const int acc = i & 1;
+      if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 13);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t accumulate = 0;
+      for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(b_full + 8 * st, (it >> 1) & 1, 14);
         if (!ok) break;
         tc_fence_after();
-        uint32_t accumulate = 0;
-        for (int s = 0; s < n_slabs && ok; ++s, ++it) {
-          const int st = it & 1;
-          ok = mbar_wait(b_full + 8 * st, (it >> 1) & 1, 14);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_tile = smem_base + (uint32_t)(s * p.planes) * PLANE_TILE_BYTES;
+        if (lane == 0) {
+          const uint32_t a_tile = smem_base + (uint32_t)(s * planes) * PLANE_TILE_BYTES;
           const uint32_t b_tile = b_base + (uint32_t)st * b_stage_bytes;
-#pragma unroll
-          for (int kk = 0; kk < SLAB_K / 16; ++kk) {
-            for (int t = 0; t < p.nterms; ++t) {
-              const uint64_t ad = kmajor_sw128_desc(a_tile + p.term_a[t] * PLANE_TILE_BYTES + kk * 32);
-              const uint64_t bd = kmajor_sw128_desc(b_tile + p.term_b[t] * PLANE_TILE_BYTES + kk * 32);
-              umma_bf16(tmem_acc + (uint32_t)(acc * TILE_N), ad, bd, p.idesc, accumulate);
-              accumulate = 1;
-            }
-          }
-          umma_commit(b_empty + 8 * st);
+          if (!(debug & 2)) issue_slab_any(planes, tmem_acc + (uint32_t)(acc * TILE_N), a_tile, b_tile, idesc, accumulate);
+          if (debug & 64) mbar_arrive(b_empty + 8 * st); else umma_commit(b_empty + 8 * st);
         }
-        umma_commit(acc_full + 8 * acc);
+        __syncwarp();
       }
+      if (ok && lane == 0) {
+        if (debug & 64) mbar_arrive(acc_full + 8 * acc); else umma_commit(acc_full + 8 * acc);
+      }
+      __syncwarp();
     }
   } else {
     const int q = warp & 3;
     const int row = m0 + q * 32 + lane;
     float* __restrict__ C = p.C;
     const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    // per-warp staging tile behind the operand buffers
+    float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + 4u * (uint32_t)p.planes * PLANE_TILE_BYTES) +
+                   (warp - 2) * 32 * STAGE_LD;
     bool ok = true;
     for (int i = 0; i < count && ok; ++i) {
       const int acc = i & 1;
       const int n0 = (nt_begin + i) * TILE_N;
       float* dst_row = C + (int64_t)row * p.ldc + n0;
       // tcgen05.ld is a warp-wide instruction: the choice of path must be uniform in the warp
-      const bool whole = __all_sync(0xffffffffu, vec_ok && row < p.M && n0 + TILE_N <= p.N);
+      const bool whole = vec_ok && m0 + q * 32 + 32 <= p.M && n0 + TILE_N <= p.N;
       if (whole) {
-        // All 128 values of this thread's row are requested before the accumulator is waited
-        // for, so the DRAM/L2 latency of C overlaps the MMAs of this tile.
+        // Global accesses of the warp are whole 128-byte row segments: lane l works on row
+        // 4*it + l/8, columns 4*(l%8).. of each 32-column chunk.  The accumulator arrives with
+        // one row per lane, so it is turned through a 32 x 32 staging tile in shared memory.
+        // All of C is requested before the accumulator is waited for: its latency overlaps the MMAs.
+        float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * p.ldc + n0 + (lane & 7) * 4;
         float4 old[TILE_N / 4];
-        if (p.beta != 0.0f) {
+        if (p.beta != 0.0f && !(p.debug & 1)) {
 #pragma unroll
-          for (int j = 0; j < TILE_N / 4; ++j) old[j] = *reinterpret_cast<const float4*>(dst_row + 4 * j);
+          for (int c = 0; c < TILE_N / 32; ++c)
+#pragma unroll
+            for (int it = 0; it < 8; ++it)
+              old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32);
         }
         ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
         if (!ok) break;
         tc_fence_after();
+        if (p.debug & 8) goto tile_done;
 #pragma unroll
         for (int c = 0; c < TILE_N / 32; ++c) {
           float v[32];
+          if (p.debug & 16) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (float)j;
+          } else
           tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 o = make_float4(p.alpha * v[4 * j], p.alpha * v[4 * j + 1], p.alpha * v[4 * j + 2], p.alpha * v[4 * j + 3]);
-            if (p.beta != 0.0f) {
-              const float4 od = old[c * 8 + j];
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&stage[(4 * it + (lane >> 3)) * STAGE_LD + (lane & 7) * 4]);
+            float4 o = make_float4(p.alpha * a4.x, p.alpha * a4.y, p.alpha * a4.z, p.alpha * a4.w);
+            if (p.beta != 0.0f && !(p.debug & 1)) {
+              const float4 od = old[c * 8 + it];
               o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
               o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
             }
-            *reinterpret_cast<float4*>(dst_row + c * 32 + 4 * j) = o;
+            if (!(p.debug & 1) || o.x == 12345.678f) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = o;
           }
+          __syncwarp();
         }
       } else {
         ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
@@ -437,6 +495,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
           }
         }
       }
+    tile_done:
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
@@ -607,7 +666,7 @@ int configure_once() {
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -628,13 +687,9 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   p.planes = A.planes;
   p.nterms = 0;
   for (int i = 0; i < A.planes; ++i)
-    for (int j = 0; j < A.planes; ++j)
-      if (i + j < A.planes) {
-        p.term_a[p.nterms] = (unsigned char)i;
-        p.term_b[p.nterms] = (unsigned char)j;
-        ++p.nterms;
-      }
+    for (int j = 0; i + j < A.planes; ++j) ++p.nterms;
   const uint32_t fmt = A.fp16 ? 0u : 1u;  // operand format: 0 = fp16, 1 = bf16
+  { const char* dbg = getenv("MQ_DEBUG_GEMM"); p.debug = dbg ? atoi(dbg) : 0; }
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
   const int stage_bytes = A.planes * 2 * PLANE_TILE_BYTES;
   int stages = (192 * 1024) / stage_bytes;
@@ -649,12 +704,27 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     // rank-<=128 update: keep A in shared memory and walk runs of n-tiles
     const int m_tiles = (int)ceil_div(d.M, TILE_M), n_tiles = (int)ceil_div(d.N, TILE_N);
     const long long tiles = d.upper_tiles_only ? (long long)n_tiles * (n_tiles + 1) / 2 : (long long)m_tiles * n_tiles;
-    // about one CTA per SM, each walking a long run, so the fixed cost of a CTA (barriers, TMEM,
-    // first operand load) is paid once per SM instead of once per tile
-    int run = (int)((tiles + 147) / 148);
-    run = run < 1 ? 1 : (run > PANEL_MAX_RUN ? PANEL_MAX_RUN : run);
+    // Pick the run length that minimises (waves of CTAs) x (fixed cost of a CTA + run): long
+    // runs pay the barrier/TMEM/first-load cost once, but the CTA count should fill the 148 SMs
+    // without a nearly empty last wave.
+    int run = 1;
+    {
+      double best = 1e30;
+      for (int cand = 1; cand <= PANEL_MAX_RUN; ++cand) {
+        long long ctas = 0;
+        for (int m = 0; m < m_tiles; ++m) {
+          const int cnt = d.upper_tiles_only ? n_tiles - m : n_tiles;
+          if (cnt > 0) ctas += (cnt + cand - 1) / cand;
+        }
+        const double waves = (double)((ctas + 147) / 148);
+        const double cost = waves * (4.0 + cand);
+        if (cost < best) { best = cost; run = cand; }
+      }
+    }
+    (void)tiles;
+    { const char* fr = getenv("MQ_DEBUG_RUN"); if (fr && atoi(fr) > 0) run = atoi(fr); }
     dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);
-    const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024;  // A: two slabs, B: two stages
+    const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + STAGE_BYTES;  // A: two slabs, B: two stages, staging
     umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, p, run);
   } else {
     umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);

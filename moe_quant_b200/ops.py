@@ -68,6 +68,27 @@ def hessian_accum(H: Tensor, x: Tensor, beta: float, alpha: float, precision: Op
                                  beta, alpha, p.math, p.split_hessian, ptr(ws), ws.numel(), stream_ptr(H.device)))
 
 
+def gemm(A: Tensor, B: Tensor, C: Tensor, alpha: float = 1.0, beta: float = 0.0, upper_tiles_only: bool = False,
+         precision: Optional[Precision] = None, split: Optional[int] = None) -> None:
+    """C <- alpha * A @ B + beta * C in place.  A (M,K), B (K,N) fp32 with any strides (views and
+    transposes are fine), C (M,N) fp32 with unit column stride."""
+    p = _prec(precision)
+    for t, n in ((A, "A"), (B, "B"), (C, "C")):
+        require_cuda(t, n)
+        if t.dtype != torch.float32 or t.dim() != 2:
+            raise MoeQuantError(f"{n} must be a 2-D fp32 tensor")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K or C.shape != (M, N) or C.stride(1) != 1:
+        raise MoeQuantError("gemm: shape mismatch")
+    sp = p.split_hinv if split is None else split
+    L = lib()
+    ws = _lib.workspace(C.device, L.mq_gemm_workspace_bytes(M, N, K, p.math, sp))
+    with torch.cuda.device(C.device):
+        check(L.mq_gemm(ptr(A), A.stride(0), A.stride(1), ptr(B), B.stride(0), B.stride(1), ptr(C), C.stride(0), M, N, K,
+                        alpha, beta, int(upper_tiles_only), p.math, sp, ptr(ws), ws.numel(), stream_ptr(C.device)))
+
+
 def hessian_prepare(H: Tensor, W: Optional[Tensor], rel_damp: float) -> Tensor:
     """In-place NaN guard, dead-channel fix, zero-column masking and damping.
     Returns the int32[4] flag tensor (nan, dead, zero columns, not-positive)."""
@@ -134,10 +155,30 @@ def absmax_scales(W: Tensor, group: int, bits: int, dtype: torch.dtype) -> Tenso
     return out
 
 
+def chol_unit_factor(H: Tensor, precision: Optional[Precision] = None, flags: Optional[Tensor] = None):
+    """In place: damped H -> Utilde = T diag(T)^-1 (unit upper), H = T T^T.  Returns (flags, diag(T))."""
+    p = _prec(precision)
+    require_cuda(H, "H")
+    C = H.shape[0]
+    L = lib()
+    diag = torch.empty(C, dtype=torch.float32, device=H.device)
+    if flags is None:
+        flags = _flags_tensor(H.device)
+    nbytes = L.mq_gemm_workspace_bytes(C, C, 128, p.math, p.split_hinv) + 4 * C + 512
+    ws = _lib.workspace(H.device, nbytes)
+    with torch.cuda.device(H.device):
+        check(L.mq_chol_unit_factor(ptr(H), C, H.stride(0), ptr(diag), p.math, p.split_hinv, ptr(flags), ptr(ws),
+                                    ws.numel(), stream_ptr(H.device)))
+    return flags, diag
+
+
 def gptq_sweep(W: Tensor, Uhat: Tensor, scale: Tensor, zero: Optional[Tensor], group: int, row_stride: int,
                group_stride: int, bits: int, dtype: torch.dtype, want_dequantized: bool = False,
-               precision: Optional[Precision] = None) -> Tuple[Tensor, Optional[Tensor]]:
+               precision: Optional[Precision] = None, W_original: Optional[Tensor] = None
+               ) -> Tuple[Tensor, Optional[Tensor]]:
     """Column sweep over the fp32 working copy W (R, C), which is destroyed.
+    With W_original (a second fp32 copy of the weights) `Uhat` must be the unit factor from
+    chol_unit_factor and the inverse-free recurrence is used.
     Returns (codes uint8 (R, C), dequantized (R, C) of `dtype` or None)."""
     p = _prec(precision)
     for t, n in ((W, "W"), (Uhat, "Uhat"), (scale, "scale")):
@@ -152,7 +193,8 @@ def gptq_sweep(W: Tensor, Uhat: Tensor, scale: Tensor, zero: Optional[Tensor], g
     ws = _lib.workspace(W.device, nbytes)
     with torch.cuda.device(W.device):
         check(L.mq_gptq_sweep(ptr(W), R, C, W.stride(0), ptr(Uhat), Uhat.stride(0), ptr(scale), ptr(zero), group,
-                              row_stride, group_stride, bits, dtype_code(dtype), ptr(codes), ptr(deq), p.math,
+                              row_stride, group_stride, bits, dtype_code(dtype), ptr(codes), ptr(deq),
+                              ptr(W_original), 0 if W_original is None else W_original.stride(0), p.math,
                               p.split_sweep, ptr(ws), ws.numel(), stream_ptr(W.device)))
     return codes, deq
 

@@ -238,3 +238,78 @@ def test_cpu_tensor_is_rejected():
 def test_bad_group_is_rejected(cuda):
     with pytest.raises(MoeQuantError):
         ops.absmax_scales(torch.zeros(4, 96, device=cuda), 64, 4, torch.float32)
+
+
+# ------------------------------------------------------------------ the GEMM engine alone, against torch fp32
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (128, 128, 64), (130, 257, 128), (300, 1000, 100), (2048, 640, 128),
+                                   (257, 129, 1000), (512, 512, 4096)])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt"])
+def test_gemm_engine_against_torch(cuda, precision, M, N, K, layout):
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    A = torch.randn(M, K, generator=g)
+    B = torch.randn(K, N, generator=g)
+    C0 = torch.randn(M, N, generator=g)
+    Ad = A.to(cuda) if layout != "tn" else A.t().contiguous().to(cuda).t()     # column-major A
+    Bd = B.to(cuda) if layout != "nt" else B.t().contiguous().to(cuda).t()     # column-major B
+    Cd = C0.clone().to(cuda)
+    ops.gemm(Ad, Bd, Cd, alpha=-0.5, beta=1.0, precision=precision)
+    want = C0.double() - 0.5 * (A.double() @ B.double())
+    err = float((Cd.cpu().double() - want).abs().max() / want.abs().max())
+    # the tensor pipe truncates when it aligns addends, so its error grows ~linearly with K;
+    # fp32 FMAs round to nearest and stay near sqrt(K) * 6e-8
+    tol = 5e-6 * max(1.0, K / 256.0) if precision.math == MATH_TENSOR else 5e-6
+    assert err < tol, f"relative error {err:.3e} (tolerance {tol:.1e})"
+
+
+def test_gemm_engine_two_plane_split_is_coarser_but_close(cuda):
+    g = torch.Generator().manual_seed(9)
+    A, B = torch.randn(256, 128, generator=g), torch.randn(128, 384, generator=g)
+    want = A.double() @ B.double()
+    errs = {}
+    for split in (1, 2, 3):
+        C = torch.zeros(256, 384, device=cuda)
+        ops.gemm(A.to(cuda), B.to(cuda), C, precision=ops.Precision(math=MATH_TENSOR), split=split)
+        errs[split] = float((C.cpu().double() - want).abs().max() / want.abs().max())
+    assert errs[1] < 2e-2 and errs[2] < 1e-4 and errs[3] < 5e-6
+    assert errs[3] < errs[2] < errs[1]
+
+
+def test_gemm_engine_upper_tiles_only(cuda, precision):
+    g = torch.Generator().manual_seed(4)
+    P = torch.randn(640, 128, generator=g)
+    C0 = torch.randn(640, 640, generator=g)
+    Cd = C0.clone().to(cuda)
+    Pd = P.to(cuda)
+    ops.gemm(Pd, Pd.t(), Cd, alpha=-1.0, beta=1.0, upper_tiles_only=True, precision=precision)
+    want = C0.double() - P.double() @ P.double().t()
+    got = Cd.cpu().double()
+    blocks = torch.arange(640) // 128
+    upper = blocks[:, None] <= blocks[None, :]
+    assert float((got - want)[upper].abs().max() / want.abs().max()) < 5e-6
+    assert torch.equal(got[~upper], C0.double()[~upper]), "tiles below the diagonal must not be touched"
+
+
+# ------------------------------------------------------------------ inverse-free form of the sweep
+def test_unit_factor_is_inverse_of_reference_factor(cuda, golden, precision):
+    H = golden.t("H_damped").clone().to(cuda)
+    flags, diag = ops.chol_unit_factor(H, precision)
+    assert flags.cpu().tolist()[3] == 0
+    Ut = H.cpu().double()
+    assert float(Ut.tril(-1).abs().max()) == 0.0 and torch.equal(Ut.diag(), torch.ones(Ut.shape[0], dtype=torch.float64))
+    eye = Ut @ golden.t("Uhat").double()
+    assert float((eye - torch.eye(Ut.shape[0], dtype=torch.float64)).abs().max()) < 2e-3
+    # diag(T)^2 reproduces the pivots: H = Utilde diag(T)^2 Utilde^T
+    back = (Ut * diag.cpu().double()[None, :] ** 2) @ Ut.t()
+    Hd = golden.t("H_damped").double()
+    assert float((back - Hd).abs().max() / Hd.abs().max()) < 1e-5
+
+
+def test_sweep_inverse_free_form_matches_reference_codes(cuda, golden, precision):
+    Wf, scale = _grid(golden)
+    R, C = Wf.shape
+    Ut = torch.linalg.inv(golden.t("Uhat").double()).float().contiguous()
+    codes, deq = ops.gptq_sweep(Wf.clone().to(cuda), Ut.to(cuda), scale.to(cuda), None, golden.group, C // golden.group, 1,
+                                4, golden.dtype, True, precision, W_original=Wf.to(cuda))
+    assert O.code_agreement(codes.cpu(), golden.t("qweight")) >= 0.999
+    want = O.dequantize_linear_weight(codes.cpu(), golden.t("scale", typed=True), golden.t("zero", typed=True))
+    assert torch.equal(deq.cpu().float(), want.float())

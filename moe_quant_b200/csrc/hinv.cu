@@ -138,7 +138,8 @@ constexpr int TT_LD = NB + 4;
 template <bool IDENTITY>
 __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict__ tblk, int64_t ldt, int64_t t_bs,
                                                         float* __restrict__ rows, int64_t ldr, int64_t r_bs,
-                                                        int nrows, int nb_full, int n_total) {
+                                                        int nrows, int nb_full, int n_total,
+                                                        uint16_t* __restrict__ planes, int64_t plane_stride, int n_planes) {
   extern __shared__ __align__(16) float smem[];
   float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
   float* dg = smem + NB * TT_LD;   // [NB] diagonal of T
@@ -235,6 +236,25 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
         }
       }
     }
+    if (!IDENTITY && planes) {
+      // the trailing update reads this panel as bf16 planes (row, k = column inside the panel)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = r0 + h;
+        if (r >= nrows) continue;
+        uint16_t hi[4], mi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) split_bf16x3(lane * 4 < nb ? a[h][q] : 0.0f, hi[q], mi[q], lo[q]);
+        uint16_t* dst = planes + (int64_t)r * NB + lane * 4;
+        *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)hi[0] | ((uint32_t)hi[1] << 16), (uint32_t)hi[2] | ((uint32_t)hi[3] << 16));
+        if (n_planes > 1)
+          *reinterpret_cast<uint2*>(dst + plane_stride) =
+              make_uint2((uint32_t)mi[0] | ((uint32_t)mi[1] << 16), (uint32_t)mi[2] | ((uint32_t)mi[3] << 16));
+        if (n_planes > 2)
+          *reinterpret_cast<uint2*>(dst + 2 * plane_stride) =
+              make_uint2((uint32_t)lo[0] | ((uint32_t)lo[1] << 16), (uint32_t)lo[2] | ((uint32_t)lo[3] << 16));
+      }
+    }
   }
 }
 
@@ -296,6 +316,17 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   MQ_TRY(configure_once());
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
+  // Tensor path: the panel solve writes its result as bf16 planes too, and the rank-128 update
+  // P P^T reads one plane set as both operands.
+  const bool tensor = math == MQ_MATH_TENSOR;
+  PlaneSet pset;
+  if (tensor) {
+    MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "factorisation: split must be 1, 2 or 3 (got %d)", split);
+    Workspace mine = eng.ws;
+    pset.base = mine.take<uint16_t>(plane_set_bytes(C, NB, split) / 2);
+    MQ_REQUIRE(pset.base, MQ_ERR_WORKSPACE, "factorisation: workspace too small for the panel planes");
+    pset.planes = split; pset.rows_pad = (int)pad_rows(C); pset.total_rows = pset.rows_pad; pset.K_pad = NB;
+  }
   // ---- factorisation, last panel first
   for (int p = P - 1; p >= 0; --p) {
     const int64_t k1 = (int64_t)p * NB;
@@ -310,7 +341,9 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
     int grid = (int)(ceil_div(k1, 16) < 148 * 2 ? ceil_div(k1, 16) : 148 * 2);
     {
       ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
-      trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0);
+      trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0,
+                                                                     tensor ? pset.base : nullptr,
+                                                                     tensor ? pset.total_rows * NB : 0, split);
     }
     MQ_LAUNCH_CHECK();
     GemmDesc g;
@@ -320,7 +353,11 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
     g.M = (int)k1; g.N = (int)k1; g.K = nb;
     g.alpha = -1.0f; g.beta = 1.0f;
     g.upper_tiles_only = 1;
-    MQ_TRY(eng.gemm(g));
+    if (tensor) {
+      MQ_TRY(gemm_tensor_planes(g, pset, pset, st));
+    } else {
+      MQ_TRY(eng.gemm(g));
+    }
   }
   // ---- T -> unit-diagonal factor
   extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
@@ -344,7 +381,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   // ---- inverse of the unit factor: invert the diagonal blocks, then merge pairs of blocks
   MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
   trsm_rows_kernel<true><<<dim3(8, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
-                                                             (int64_t)NB * (ldu + 1), NB, NB, (int)C);
+                                                             (int64_t)NB * (ldu + 1), NB, NB, (int)C, nullptr, 0, 0);
   MQ_LAUNCH_CHECK();
   for (int64_t s = NB; s < C; s *= 2) {
     const int batch = (int)ceil_div(C - s, 2 * s);

@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     const float* __restrict__ scale, const float* __restrict__ zero, int64_t group, int64_t s_rs, int64_t s_gs,
     float maxq, float zero_default, uint8_t* __restrict__ codes, int64_t C,
     typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb,
-    const float* __restrict__ Worig, int64_t ldwo) {
+    const float* __restrict__ Worig, int64_t ldwo, uint16_t* __restrict__ err_planes, int64_t plane_stride,
+    int n_planes) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
@@ -104,7 +105,22 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     }
   }
   // columns past nb of a narrow last tile hold zeros so the GEMM may read all 128
-  *reinterpret_cast<float4*>(err + (int64_t)r * TILE + lane * 4) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+  if (err_planes) {
+    // the tensor-core update reads the errors as bf16 planes: write them in that form directly
+    uint16_t h[4], m[4], l[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) split_bf16x3(ev[t], h[t], m[t], l[t]);
+    uint16_t* dst = err_planes + (int64_t)r * TILE + lane * 4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+    if (n_planes > 1)
+      *reinterpret_cast<uint2*>(dst + plane_stride) =
+          make_uint2((uint32_t)m[0] | ((uint32_t)m[1] << 16), (uint32_t)m[2] | ((uint32_t)m[3] << 16));
+    if (n_planes > 2)
+      *reinterpret_cast<uint2*>(dst + 2 * plane_stride) =
+          make_uint2((uint32_t)l[0] | ((uint32_t)l[1] << 16), (uint32_t)l[2] | ((uint32_t)l[3] << 16));
+  } else {
+    *reinterpret_cast<float4*>(err + (int64_t)r * TILE + lane * 4) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+  }
 }
 
 int configure_once() {
@@ -124,7 +140,9 @@ int configure_once() {
 }  // namespace
 
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
-  return align_up((size_t)R * TILE * sizeof(float), 256) + engine_workspace_bytes(R, C, TILE, math, split);
+  size_t bytes = align_up((size_t)R * TILE * sizeof(float), 256);
+  if (math == MQ_MATH_TENSOR) bytes += plane_set_bytes(R, TILE, split) + plane_set_bytes(C, C, split);
+  return bytes;
 }
 
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
@@ -134,6 +152,22 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   float* err = ws.take<float>((size_t)R * TILE);
   MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
   Engine eng(math, split, ws, st);
+  // Tensor path: the factor is cut into transposed planes once (row n, k -> U[k][n]); the lazy
+  // update of tile i1 then reads the window k in [i1, i1+128), rows n >= i2 of those planes,
+  // and the sweep kernel writes its errors as planes itself.  No per-tile conversion passes.
+  PlaneSet err_set, u_set;
+  const bool tensor = math == MQ_MATH_TENSOR;
+  if (tensor) {
+    MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "mq_gptq_sweep: split must be 1, 2 or 3 (got %d)", split);
+    uint16_t* ep = ws.take<uint16_t>(plane_set_bytes(R, TILE, split) / 2);
+    uint16_t* up = ws.take<uint16_t>(plane_set_bytes(C, C, split) / 2);
+    MQ_REQUIRE(ep && up, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small for the operand planes");
+    err_set.base = ep; err_set.planes = split; err_set.rows_pad = (int)pad_rows(R); err_set.total_rows = err_set.rows_pad;
+    err_set.K_pad = TILE;
+    MQ_TRY(make_planes_f32(Uhat, 1, ldu, (int)C, (int)C, split, up, &u_set, st));
+  }
+  uint16_t* const ep_arg = tensor ? err_set.base : nullptr;
+  const int64_t ep_stride = tensor ? err_set.total_rows * TILE : 0;
   const float maxq = (float)((1 << bits) - 1);
   const float zero_default = 0.5f * (float)(1 << bits);
   const int grid = (int)ceil_div(R, SWEEP_THREADS / 32);
@@ -147,17 +181,17 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       case MQ_F32:
         sweep_tile_kernel<MQ_F32><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<float*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo);
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
         break;
       case MQ_BF16:
         sweep_tile_kernel<MQ_BF16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                    maxq, zero_default, codes, C,
-                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo);
+                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
         break;
       default:
         sweep_tile_kernel<MQ_F16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo);
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
     }
     }
     MQ_LAUNCH_CHECK();
@@ -169,7 +203,14 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       g.C = W + i2; g.ldc = ldw;
       g.M = (int)R; g.N = (int)(C - i2); g.K = nb;
       g.alpha = 1.0f; g.beta = 1.0f;
-      MQ_TRY(eng.gemm(g));
+      if (tensor) {
+        PlaneSet b = u_set;
+        b.row0 = i2;
+        b.k0 = (int)i1;
+        MQ_TRY(gemm_tensor_planes(g, err_set, b, st));
+      } else {
+        MQ_TRY(eng.gemm(g));
+      }
     }
   }
   return MQ_OK;

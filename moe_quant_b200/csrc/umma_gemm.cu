@@ -43,6 +43,7 @@ struct UmmaParams {
   int upper_tiles_only, a_upper, b_upper;
   int n_total, n_step, k_follows_n;
   int a_rows_pad, b_rows_pad;  // rows each batch occupies in the stacked plane buffers
+  int a_row0, a_k0, b_row0, b_k0;  // origin of the operand windows inside their plane buffers
   int planes, nterms, stages;
   uint32_t idesc;
   int debug;  // timing experiments only: 1 = epilogue touches no global memory, 2 = no MMA is issued, 4 = no B loads
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      const int a_row = b * p.a_rows_pad + m0, b_row = b * p.b_rows_pad + n0;
+      const int a_row = b * p.a_rows_pad + m0 + p.a_row0, b_row = b * p.b_rows_pad + n0 + p.b_row0;
       for (int s = 0; s < n_slabs; ++s) {
         const int st = s % p.stages;
         if (s >= p.stages && !mbar_wait(empty0 + 8 * st, ((s / p.stages) - 1) & 1, 1)) break;
@@ -224,8 +225,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
         const uint32_t dst = smem_base + st * stage_bytes;
         const int k = k_lo + s * SLAB_K;
         for (int pl = 0; pl < p.planes; ++pl) {
-          tma_load_3d(dst + pl * PLANE_TILE_BYTES, &map_a, full0 + 8 * st, k, a_row, pl);
-          tma_load_3d(dst + (p.planes + pl) * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, k, b_row, pl);
+          tma_load_3d(dst + pl * PLANE_TILE_BYTES, &map_a, full0 + 8 * st, k + p.a_k0, a_row, pl);
+          tma_load_3d(dst + (p.planes + pl) * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, k + p.b_k0, b_row, pl);
         }
       }
     }
@@ -366,7 +367,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
       mbar_expect_tx(a_full, a_bytes);
       for (int s = 0; s < n_slabs; ++s)
         for (int pl = 0; pl < planes; ++pl)
-          tma_load_3d(smem_base + (uint32_t)(s * planes + pl) * PLANE_TILE_BYTES, &map_a, a_full, s * SLAB_K, m0, pl);
+          tma_load_3d(smem_base + (uint32_t)(s * planes + pl) * PLANE_TILE_BYTES, &map_a, a_full, s * SLAB_K + p.a_k0,
+                      m0 + p.a_row0, pl);
     }
     int it = 0;
     bool ok = true;
@@ -382,7 +384,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
             mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
             for (int pl = 0; pl < planes; ++pl)
               tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
-                          s * SLAB_K, b_row, pl);
+                          s * SLAB_K + p.b_k0, b_row + p.b_row0, pl);
           }
         }
         __syncwarp();
@@ -596,16 +598,6 @@ int get_encoder(EncodeTiledFn* out) {
   return MQ_OK;
 }
 
-// Planes of one operand: [planes][total_rows][K_pad] 16-bit elements.
-struct PlaneSet {
-  uint16_t* base = nullptr;
-  int planes = 0;
-  int64_t total_rows = 0;  // batch * rows_pad
-  int rows_pad = 0;
-  int K_pad = 0;
-  bool fp16 = false;
-};
-
 int encode_map(const PlaneSet& ps, CUtensorMap* map) {
   EncodeTiledFn enc;
   MQ_TRY(get_encoder(&enc));
@@ -684,6 +676,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   p.upper_tiles_only = d.upper_tiles_only; p.a_upper = d.a_upper; p.b_upper = d.b_upper;
   p.n_total = d.n_total; p.n_step = d.n_step; p.k_follows_n = d.k_follows_n;
   p.a_rows_pad = A.rows_pad; p.b_rows_pad = B.rows_pad;
+  p.a_row0 = (int)A.row0; p.a_k0 = A.k0; p.b_row0 = (int)B.row0; p.b_k0 = B.k0;
   p.planes = A.planes;
   p.nterms = 0;
   for (int i = 0; i < A.planes; ++i)
@@ -734,6 +727,19 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
 }
 
 }  // namespace
+
+int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStream_t st) {
+  if (d.M <= 0 || d.N <= 0 || d.batch <= 0) return MQ_OK;
+  MQ_REQUIRE(A.planes == B.planes && A.planes >= 1 && A.planes <= 3 && A.fp16 == B.fp16, MQ_ERR_ARGUMENT,
+             "tensor engine: operand plane sets do not match");
+  return launch_umma(d, A, B, st);
+}
+
+int make_planes_f32(const float* src, int64_t rs, int64_t cs, int rows, int K, int planes, uint16_t* dst, PlaneSet* out,
+                    cudaStream_t st) {
+  Workspace ws(dst, plane_set_bytes(rows, K, planes));
+  return make_planes(src, MQ_F32, rs, cs, 0, rows, K, 1, planes, 0, 0, 0, 0, ws, out, st);
+}
 
 size_t engine_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split) {
   if (math != MQ_MATH_TENSOR) return 0;

@@ -155,7 +155,7 @@ def run_b200(args):
     import torch.distributed as dist
     import torch.nn as nn
 
-    from moe_quant_b200 import GPTQ, _lib, ops, synthetic
+    from moe_quant_b200 import GPTQ, _lib, ops, quantize_many, synthetic
 
     world, rank, local = _dist()
     if not torch.cuda.is_available():
@@ -202,20 +202,31 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- timed region: K quantize() calls
+    # ---- timed region: K quantize() calls, issued round-robin on `streams` CUDA streams
+    # (independent experts: their kernel chains overlap on the GPU)
+    n_streams = max(1, args.streams)
     handles = make_handles(warmup + steps)
-    for h in handles[:warmup]:
-        h.quantize(BITS)
+    quantize_many(handles[:warmup], BITS, streams=n_streams)
     barrier()
     launches0 = _lib.lib().mq_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         ev0.record()
-        results = [h.quantize(BITS) for h in handles[warmup:]]
+        results = quantize_many(handles[warmup:], BITS, streams=n_streams)
         ev1.record()
         barrier()
     ms_total = ev0.elapsed_time(ev1)
     launches = _lib.lib().mq_launch_count() - launches0
+    # the same K calls one after the other on one stream (what a plain `for handle: quantize` loop gets)
+    seq_handles = make_handles(steps)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    seq_results = [h.quantize(BITS) for h in seq_handles]
+    s1.record()
+    barrier()
+    ms_single = s0.elapsed_time(s1)
+    del seq_handles, seq_results
     issues = sum(h.has_hessian_issues() for h in handles)
     fault = _lib.engine_fault()
     del handles, results
@@ -319,7 +330,8 @@ def run_b200(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "experts_rotated": n_experts, "tokens_per_expert": tokens,
                        "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
-                       "parallelism": f"ep{world}", "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
+                       "parallelism": f"ep{world}", "streams": n_streams,
+                       "single_stream_layers_per_s_per_gpu": steps / (ms_single / 1e3), "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
             "roofline": roofline, "kernel_time_shares": shares,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "layers/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -339,6 +351,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--streams", type=int, default=4, help="CUDA streams the independent layers are spread over")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -139,9 +139,11 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer that only ever grows.  Work is stream-ordered, so
-    consecutive calls on one stream may share it."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """A scratch buffer per (device, current stream) that only ever grows.  Work is
+    stream-ordered, so consecutive calls on one stream may share it; calls on different
+    streams may overlap on the GPU and therefore get different buffers."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         _workspaces[key] = None

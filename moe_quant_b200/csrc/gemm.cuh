@@ -20,6 +20,7 @@ struct GemmDesc {
   float alpha = 1.0f, beta = 0.0f;
   // Structure that lets whole tiles or k-ranges be skipped:
   int upper_tiles_only = 0;  // skip output tiles that lie entirely below the diagonal
+  int mirror_to_lower = 0;   // with upper_tiles_only on a symmetric result: also write C[n,m] = C[m,n] (tensor path)
   int a_upper = 0;           // A is upper triangular (A[m,k] == 0 for k < m): k starts at the tile's first row
   int b_upper = 0;           // B is upper triangular (B[k,n] == 0 for k > n): k stops at the tile's last column
   // Batched form: operand b lives at base + b * stride (elements of the operand type).

@@ -34,6 +34,8 @@ constexpr int TILE_M = 128, TILE_N = 128, SLAB_K = 64;
 constexpr int PLANE_TILE_BYTES = TILE_M * SLAB_K * 2;  // 16 KB
 constexpr int GEMM_THREADS = 192;
 constexpr int MAX_TERMS = 6;
+constexpr int STAGE_LD = 36;                        // floats per row of an epilogue staging tile
+constexpr int STAGE_BYTES = 4 * 32 * STAGE_LD * 4;  // four epilogue warps
 
 struct UmmaParams {
   float* C;
@@ -46,6 +48,7 @@ struct UmmaParams {
   int a_row0, a_k0, b_row0, b_k0;  // origin of the operand windows inside their plane buffers
   int planes, nterms, stages;
   uint32_t idesc;
+  int mirror;  // symmetric result: every block above the diagonal is also stored transposed
   int debug;  // timing experiments only: 1 = epilogue touches no global memory, 2 = no MMA is issued, 4 = no B loads
 };
 
@@ -249,43 +252,107 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
   } else {
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const bool have_acc = n_slabs > 0;
-    bool ok = true;
-    if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
-    tc_fence_after();
     float* __restrict__ C = p.C + (int64_t)b * p.c_bs;
     const int row = m0 + q * 32 + lane;
     const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-    if (ok) {
-#pragma unroll 1
-      for (int c = 0; c < TILE_N / 32; ++c) {
-        float v[32];
-        if (have_acc) {
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-        } else {
+    // whole 32 x 128 quadrant in range: coalesced path (uniform in the warp, tcgen05.ld is warp-wide)
+    const bool whole = vec_ok && m0 + q * 32 + 32 <= p.M && n0 + TILE_N <= N;
+    bool ok = true;
+    if (whole) {
+      // lane l handles row 4*it + l/8, columns 4*(l%8).. of each 32-column chunk: every global
+      // access of the warp is four full 128-byte row segments.  C is requested before the
+      // accumulator is waited for.
+      float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * p.ldc + n0 + (lane & 7) * 4;
+      float4 old[TILE_N / 4];
+      if (p.beta != 0.0f) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-        }
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < N) {
-          float* dst = C + (int64_t)row * p.ldc + col0;
-          if (vec_ok && col0 + 32 <= N) {
+        for (int c = 0; c < TILE_N / 32; ++c)
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
-              if (p.beta != 0.0f) {
-                const float4 old = *reinterpret_cast<const float4*>(dst + j);
-                o.x = fmaf(p.beta, old.x, o.x); o.y = fmaf(p.beta, old.y, o.y);
-                o.z = fmaf(p.beta, old.z, o.z); o.w = fmaf(p.beta, old.w, o.w);
-              }
-              *reinterpret_cast<float4*>(dst + j) = o;
-            }
+          for (int it = 0; it < 8; ++it) old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32);
+      }
+      if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
+      tc_fence_after();
+      // every MMA has completed, so the operand stages are free: stage 0 becomes the staging tiles
+      float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_LD;
+      // Symmetric result (p.mirror): the upper triangle is authoritative and every 32 x 32 block
+      // above the diagonal is also stored transposed.  A tile on the diagonal holds both halves
+      // from the MMA, but A_i B_j and A_j B_i are summed in different orders there, so its blocks
+      // below the diagonal are not stored and its diagonal blocks are symmetrised, which makes
+      // C[n,m] == C[m,n] bit for bit.
+      const bool diag_tile = p.mirror && n0 == m0;
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          float v[32];
+          if (have_acc) {
+            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
           } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+          }
+          const bool store_direct = !(diag_tile && c <= q);
+          const bool store_mirror = p.mirror && (n0 > m0 || c > q);
+          const bool symmetrise = diag_tile && c == q;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            float* sp = &stage[(4 * it + (lane >> 3)) * STAGE_LD + (lane & 7) * 4];
+            const float4 a4 = *reinterpret_cast<const float4*>(sp);
+            float4 o = make_float4(p.alpha * a4.x, p.alpha * a4.y, p.alpha * a4.z, p.alpha * a4.w);
+            if (p.beta != 0.0f) {
+              const float4 od = old[c * 8 + it];
+              o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
+              o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
+            }
+            if (store_direct) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = o;
+            if (p.mirror) *reinterpret_cast<float4*>(sp) = o;  // keep the final values for the stores below
+          }
+          __syncwarp();
+          if (symmetrise) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = 4 * it + (lane >> 3), cc = (lane & 7) * 4;
+              float e[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) e[t] = (cc + t >= r) ? stage[r * STAGE_LD + cc + t] : stage[(cc + t) * STAGE_LD + r];
+              *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = make_float4(e[0], e[1], e[2], e[3]);
+            }
+          }
+          if (store_mirror) {
+            // C[n0 + 32c + i][m0 + 32q + l] = final[l][i]: one 128-byte row segment per i
+            float* mq = C + (int64_t)(n0 + c * 32) * p.ldc + m0 + q * 32 + lane;
+#pragma unroll 8
+            for (int i = 0; i < 32; ++i) mq[(int64_t)i * p.ldc] = stage[lane * STAGE_LD + i];
+          }
+          __syncwarp();
+        }
+      }
+    } else {
+      if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
+      tc_fence_after();
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          float v[32];
+          if (have_acc) {
+            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+          }
+          const int col0 = n0 + c * 32;
+          if (row < p.M && col0 < N) {
+            float* dst = C + (int64_t)row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < N) {
                 float o = p.alpha * v[j];
                 if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
-                dst[j] = o;
+                if (!(p.mirror && col0 + j < row)) dst[j] = o;   // symmetric result: the upper triangle is authoritative
+                if (p.mirror && col0 + j > row) C[(int64_t)(col0 + j) * p.ldc + row] = o;
               }
             }
           }
@@ -310,8 +377,6 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
 //   warps 2..5 : epilogue of tile i (TMEM -> registers -> C += ...) while tile i+1 is multiplied
 // so the read-modify-write of C, the B loads and the tensor pipe overlap.
 constexpr int PANEL_MAX_RUN = 16;
-constexpr int STAGE_LD = 36;                               // floats per row of an epilogue staging tile
-constexpr int STAGE_BYTES = 4 * 32 * STAGE_LD * 4;         // four epilogue warps
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -675,6 +740,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   p.alpha = d.alpha; p.beta = d.beta;
   p.upper_tiles_only = d.upper_tiles_only; p.a_upper = d.a_upper; p.b_upper = d.b_upper;
   p.n_total = d.n_total; p.n_step = d.n_step; p.k_follows_n = d.k_follows_n;
+  p.mirror = d.mirror_to_lower;
   p.a_rows_pad = A.rows_pad; p.b_rows_pad = B.rows_pad;
   p.a_row0 = (int)A.row0; p.a_k0 = A.k0; p.b_row0 = (int)B.row0; p.b_k0 = B.k0;
   p.planes = A.planes;
@@ -693,7 +759,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   double flop_alg = 0.0, flop_issued = 0.0;
   if (g_profile_on) gemm_work(d, SLAB_K, &flop_alg, &flop_issued, p.nterms);
   ProfScope prof(PROF_UMMA_GEMM, flop_alg, flop_issued, st);
-  if (d.K <= 2 * SLAB_K && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.K > 0) {
+  if (d.K <= 2 * SLAB_K && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.K > 0 && !d.mirror_to_lower) {
     // rank-<=128 update: keep A in shared memory and walk runs of n-tiles
     const int m_tiles = (int)ceil_div(d.M, TILE_M), n_tiles = (int)ceil_div(d.N, TILE_N);
     const long long tiles = d.upper_tiles_only ? (long long)n_tiles * (n_tiles + 1) / 2 : (long long)m_tiles * n_tiles;
@@ -790,8 +856,8 @@ int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64
     A.base = ws.take<uint16_t>((size_t)A.rows_pad * SLAB_K);
     MQ_REQUIRE(A.base, MQ_ERR_WORKSPACE, "mq_hessian_accum: workspace too small");
   }
-  MQ_TRY(launch_umma(g, A, A, st));
-  return mirror_upper_to_lower(H, C, ldh, st);
+  g.mirror_to_lower = 1;  // the epilogue stores every block above the diagonal transposed as well
+  return launch_umma(g, A, A, st);
 }
 
 }  // namespace mq

@@ -291,6 +291,46 @@ class GPTQ:
         return U
 
 
+_stream_pools: dict = {}
+
+
+def _side_streams(device: torch.device, n: int):
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    pool = _stream_pools.setdefault(key, [])
+    while len(pool) < n:
+        pool.append(torch.cuda.Stream(device=device))
+    return pool[:n]
+
+
+@torch.no_grad()
+def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 4) -> List[Tuple[Tensor, Tensor, Tensor]]:
+    """Quantizes independent, non-distributed handles (the routed experts of a rank,
+    quant.py:351-387) round-robin on `streams` CUDA streams.  One layer's GPTQ is a long chain of
+    dependent kernels, many of them too small to fill 148 SMs; chains of different layers have no
+    dependency on each other, so running a few side by side fills the machine.  Results are the
+    same tensors handle.quantize(bits) returns, in the order of `handles`, ready for use on the
+    stream that was current at the call."""
+    if not handles:
+        return []
+    if any(h.is_distributed for h in handles):
+        raise MoeQuantError("quantize_many is for non-distributed handles; distributed ones broadcast their results")
+    device = handles[0].W_device
+    current = torch.cuda.current_stream(device)
+    pool = _side_streams(device, max(1, min(streams, len(handles))))
+    for s in pool:
+        s.wait_stream(current)
+    out = []
+    for i, h in enumerate(handles):
+        with torch.cuda.stream(pool[i % len(pool)]):
+            out.append(h.quantize(bits))
+    for s in pool:
+        current.wait_stream(s)
+    for res in out:
+        for t in res:
+            t.record_stream(current)
+    return out
+
+
 @torch.no_grad()
 def quantize_tied(handles: Sequence[GPTQ], bits: int) -> List[Tuple[Tensor, Tensor, Tensor]]:
     """Quantizes handles that share one Hessian (gate_proj/up_proj of an expert,

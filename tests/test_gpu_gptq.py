@@ -163,3 +163,24 @@ def test_full_size_layer_properties(cuda, precision):
     words = ops.pack_int4(q)
     shifts = torch.arange(8, device=cuda, dtype=torch.int32) * 4
     assert torch.equal(((words.unsqueeze(-1) >> shifts) & 0xF).reshape(R, C).to(torch.uint8), q)
+
+
+def test_quantize_many_streams_match_sequential(cuda, precision):
+    from moe_quant_b200 import quantize_many
+    R, C, N = 64, 512, 600
+    Ws = [synthetic.layer_weight(R, C, 20 + i, torch.bfloat16) for i in range(5)]
+    Xs = [synthetic.activations(N + 37 * i, C, 40 + i, torch.bfloat16) for i in range(5)]
+
+    def handles():
+        hs = []
+        for W, X in zip(Ws, Xs):
+            h = GPTQ(_layer(W, cuda), 128, True, 1e-2, 128, precision=precision)
+            h.update(X.to(cuda))
+            hs.append(h)
+        return hs
+
+    seq = [h.quantize(4) for h in handles()]
+    par = quantize_many(handles(), 4, streams=3)
+    torch.cuda.synchronize()
+    for (q1, s1, z1), (q2, s2, z2) in zip(seq, par):
+        assert torch.equal(q1, q2) and torch.equal(s1, s2) and torch.equal(z1, z2)

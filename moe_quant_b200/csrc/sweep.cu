@@ -78,17 +78,39 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     wo[0] = v.x; wo[1] = v.y; wo[2] = v.z; wo[3] = v.w;
   }
 
+  // x / s through the reciprocal and one correction step (the final stage of a correctly rounded
+  // division): a few FMAs on the serial chain instead of the full division sequence.
+  float rs[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) rs[t] = 1.0f / sc[t];
+
   const int n_quads = nb >> 2;
   for (int jq = 0; jq < n_quads; ++jq) {
+    // The four columns of quad jq belong to lane jq and depend on each other only through the
+    // 4 x 4 diagonal block of U, so that lane can run them back to back without a shuffle.  Every
+    // lane runs the same four steps on a copy of its own values against that block (uniform
+    // code, no divergence); only lane jq's results are real.  Its four errors are then broadcast
+    // and applied to the true running weights of all lanes, in the same order, with the same
+    // FMAs the one-column-at-a-time recurrence would use.
+    float wl[4] = {w[0], w[1], w[2], w[3]};
+    float e4[4];
+    const float* ud = &ublk[(jq * 4) * TILE + jq * 4];  // diagonal block, same address for all lanes
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      // Every lane evaluates the grid on its own element; only lane jq's value is used.
-      const float x = w[t];
-      const float q = fminf(fmaxf(floorf((x / sc[t] + zr[t]) + 0.5f), 0.0f), maxq);
+      const float x = wl[t];
+      float d = x * rs[t];
+      d = fmaf(fmaf(-sc[t], d, x), rs[t], d);
+      const float q = fminf(fmaxf(floorf((d + zr[t]) + 0.5f), 0.0f), maxq);
       const float y = round_through<DT>((q - zr[t]) * sc[t]);
       const float e = inverse_free ? (wo[t] - y) : (y - x);
+      e4[t] = e;
       if (lane == jq) { qv[t] = q; yv[t] = y; ev[t] = e; }
-      const float eb = __shfl_sync(0xffffffffu, e, jq);
+#pragma unroll
+      for (int t2 = t + 1; t2 < 4; ++t2) wl[t2] = fmaf(ud[t * TILE + t2], e, wl[t2]);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float eb = __shfl_sync(0xffffffffu, e4[t], jq);
       const float4 u = *reinterpret_cast<const float4*>(&ublk[(jq * 4 + t) * TILE + lane * 4]);
       w[0] = fmaf(u.x, eb, w[0]);
       w[1] = fmaf(u.y, eb, w[1]);

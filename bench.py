@@ -64,7 +64,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -284,12 +284,15 @@ def run_b200(args):
     # ---- end to end through the handle with host buffers
     Wh = [w.cpu().pin_memory() for w in weights]
     Xh = synthetic.activations(TOKENS, C, seed, torch.bfloat16).pin_memory()
-    q_host = torch.empty(R, C, dtype=torch.uint8).pin_memory()
-    s_host = torch.empty(R, C // GROUP, dtype=torch.bfloat16).pin_memory()
+    # one set of pinned result buffers per stream: steps on different streams overlap
+    pool = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+    q_host = [torch.empty(R, C, dtype=torch.uint8).pin_memory() for _ in pool]
+    s_host = [torch.empty(R, C // GROUP, dtype=torch.bfloat16).pin_memory() for _ in pool]
     h2d = Wh[0].numel() * 2 + Xh.numel() * 2
-    d2h = q_host.numel() + s_host.numel() * 2
+    d2h = q_host[0].numel() + s_host[0].numel() * 2
 
     def e2e_step(i):
+        k = i % n_streams
         W = Wh[i % n_experts].to(dev, non_blocking=True)
         Xd = Xh.to(dev, non_blocking=True)
         layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
@@ -297,18 +300,26 @@ def run_b200(args):
         h = GPTQ(layer, GROUP, True, 1e-2, 128)
         h.update(Xd)
         q, s, _z = h.quantize(BITS)
-        q_host.copy_(q, non_blocking=True)
-        s_host.copy_(s, non_blocking=True)
+        q_host[k].copy_(q, non_blocking=True)
+        s_host[k].copy_(s, non_blocking=True)
         h.reset()
 
+    def e2e_run(n):
+        cur = torch.cuda.current_stream(dev)
+        for st in pool:
+            st.wait_stream(cur)
+        for i in range(n):
+            with torch.cuda.stream(pool[i % n_streams]):
+                e2e_step(i)
+        for st in pool:
+            cur.wait_stream(st)
+
     e2e_steps = steps
-    for i in range(warmup):
-        e2e_step(i)
+    e2e_run(max(warmup, n_streams))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
+    e2e_run(e2e_steps)
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -349,7 +360,7 @@ def run_b200(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams the independent layers are spread over")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])

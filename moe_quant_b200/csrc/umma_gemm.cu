@@ -19,7 +19,6 @@
 // Every mbarrier wait is bounded; a wait that expires records a code in g_engine_fault,
 // the kernel still frees its TMEM and returns.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include "engine.cuh"
 #include "profile.cuh"
@@ -49,7 +48,6 @@ struct UmmaParams {
   int planes, nterms, stages;
   uint32_t idesc;
   int mirror;  // symmetric result: every block above the diagonal is also stored transposed
-  int debug;  // timing experiments only: 1 = epilogue touches no global memory, 2 = no MMA is issued, 4 = no B loads
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -407,7 +405,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   const uint32_t acc_full = smem_u32(&bars[5]), acc_empty = smem_u32(&bars[7]);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int planes = p.planes, debug = p.debug;
+  const int planes = p.planes;
   const uint32_t idesc = p.idesc;
   if (threadIdx.x == 0) {
     mbar_init(a_full, 1);
@@ -443,14 +441,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         const int st = it & 1;
         if (it >= 2 && !mbar_wait(b_empty + 8 * st, ((it >> 1) - 1) & 1, 11)) { ok = false; break; }
         if (lane == 0) {
-          if (debug & 4) {
-            mbar_arrive(b_full + 8 * st);
-          } else {
-            mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
-            for (int pl = 0; pl < planes; ++pl)
-              tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
-                          s * SLAB_K + p.b_k0, b_row + p.b_row0, pl);
-          }
+          mbar_expect_tx(b_full + 8 * st, b_stage_bytes);
+          for (int pl = 0; pl < planes; ++pl)
+            tma_load_3d(b_base + (uint32_t)st * b_stage_bytes + (uint32_t)pl * PLANE_TILE_BYTES, &map_b, b_full + 8 * st,
+                        s * SLAB_K + p.b_k0, b_row + p.b_row0, pl);
         }
         __syncwarp();
       }
@@ -472,13 +466,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         if (lane == 0) {
           const uint32_t a_tile = smem_base + (uint32_t)(s * planes) * PLANE_TILE_BYTES;
           const uint32_t b_tile = b_base + (uint32_t)st * b_stage_bytes;
-          if (!(debug & 2)) issue_slab_any(planes, tmem_acc + (uint32_t)(acc * TILE_N), a_tile, b_tile, idesc, accumulate);
-          if (debug & 64) mbar_arrive(b_empty + 8 * st); else umma_commit(b_empty + 8 * st);
+          issue_slab_any(planes, tmem_acc + (uint32_t)(acc * TILE_N), a_tile, b_tile, idesc, accumulate);
+          umma_commit(b_empty + 8 * st);  // the stage is free once these MMAs have read it
         }
         __syncwarp();
       }
       if (ok && lane == 0) {
-        if (debug & 64) mbar_arrive(acc_full + 8 * acc); else umma_commit(acc_full + 8 * acc);
+        umma_commit(acc_full + 8 * acc);
       }
       __syncwarp();
     }
@@ -504,7 +498,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         // All of C is requested before the accumulator is waited for: its latency overlaps the MMAs.
         float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * p.ldc + n0 + (lane & 7) * 4;
         float4 old[TILE_N / 4];
-        if (p.beta != 0.0f && !(p.debug & 1)) {
+        if (p.beta != 0.0f) {
 #pragma unroll
           for (int c = 0; c < TILE_N / 32; ++c)
 #pragma unroll
@@ -514,14 +508,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
         if (!ok) break;
         tc_fence_after();
-        if (p.debug & 8) goto tile_done;
 #pragma unroll
         for (int c = 0; c < TILE_N / 32; ++c) {
           float v[32];
-          if (p.debug & 16) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (float)j;
-          } else
           tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -531,12 +520,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
           for (int it = 0; it < 8; ++it) {
             const float4 a4 = *reinterpret_cast<const float4*>(&stage[(4 * it + (lane >> 3)) * STAGE_LD + (lane & 7) * 4]);
             float4 o = make_float4(p.alpha * a4.x, p.alpha * a4.y, p.alpha * a4.z, p.alpha * a4.w);
-            if (p.beta != 0.0f && !(p.debug & 1)) {
+            if (p.beta != 0.0f) {
               const float4 od = old[c * 8 + it];
               o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
               o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
             }
-            if (!(p.debug & 1) || o.x == 12345.678f) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = o;
+            *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = o;
           }
           __syncwarp();
         }
@@ -562,7 +551,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
           }
         }
       }
-    tile_done:
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
@@ -748,7 +736,6 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   for (int i = 0; i < A.planes; ++i)
     for (int j = 0; i + j < A.planes; ++j) ++p.nterms;
   const uint32_t fmt = A.fp16 ? 0u : 1u;  // operand format: 0 = fp16, 1 = bf16
-  { const char* dbg = getenv("MQ_DEBUG_GEMM"); p.debug = dbg ? atoi(dbg) : 0; }
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
   const int stage_bytes = A.planes * 2 * PLANE_TILE_BYTES;
   int stages = (192 * 1024) / stage_bytes;
@@ -781,7 +768,6 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
       }
     }
     (void)tiles;
-    { const char* fr = getenv("MQ_DEBUG_RUN"); if (fr && atoi(fr) > 0) run = atoi(fr); }
     dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);
     const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + STAGE_BYTES;  // A: two slabs, B: two stages, staging
     umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, p, run);

@@ -257,6 +257,9 @@ def run_b200(args):
             roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
                         "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"], "traffic": None,
                         "issued_tflops": v["work2"] / (v["ms"] / 1e3) / 1e12,
+                        "frac_issued": v["work2"] / (v["ms"] / 1e3) / 1e12 / peaks["tensor_sustained"],
+                        "note": "achieved counts fp32-equivalent flop (2MNK on kept tiles); every fp32 product is "
+                                "six bf16 tensor products (3 planes), which is what issued_tflops / frac_issued count",
                         "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
                         "peak_source": peaks["source"] + " (sustained bf16)"}
         else:

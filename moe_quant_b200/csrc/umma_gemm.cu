@@ -174,11 +174,16 @@ __device__ __forceinline__ void issue_slab_any(int planes, uint32_t tmem_d, uint
 }
 
 // ---------------------------------------------------------------- the GEMM kernel
+// TN = 128: any number of planes.  TN = 256: one plane only (bf16/fp16 activations of the
+// Hessian); the wider tile halves the A bytes streamed per flop, which is what limits a
+// one-product GEMM (4 MMAs per 64-wide slab), and leaves room for a 4-stage ring.
+template <int TN>
 __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ CUtensorMap map_b,
                                                                  const UmmaParams p) {
+  constexpr int B_TILE_BYTES = TN * SLAB_K * 2;
   const int b = blockIdx.z;
-  const int m0 = blockIdx.y * TILE_M, n0 = blockIdx.x * TILE_N;
+  const int m0 = blockIdx.y * TILE_M, n0 = blockIdx.x * TN;
   int N = p.N, K = p.K;
   if (p.n_step) {
     int left = p.n_total - b * p.n_step;
@@ -186,21 +191,21 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     if (p.k_follows_n) K = N;
   }
   if (N <= 0 || n0 >= N || m0 >= p.M) return;
-  if (p.upper_tiles_only && n0 + TILE_N <= m0) return;
+  if (p.upper_tiles_only && n0 + TN <= m0) return;
   const int k_lo = p.a_upper ? (m0 / SLAB_K) * SLAB_K : 0;
   int k_hi = K;
-  if (p.b_upper && n0 + TILE_N < k_hi) k_hi = n0 + TILE_N;
+  if (p.b_upper && n0 + TN < k_hi) k_hi = n0 + TN;
   const int n_slabs = k_hi > k_lo ? (k_hi - k_lo + SLAB_K - 1) / SLAB_K : 0;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
-  const uint32_t stage_bytes = (uint32_t)p.planes * 2u * PLANE_TILE_BYTES;
+  const int planes = p.planes;
+  const uint32_t stage_bytes = (uint32_t)planes * (PLANE_TILE_BYTES + B_TILE_BYTES);
   __shared__ __align__(8) uint64_t bars[2 * 4 + 1];
   __shared__ uint32_t tmem_slot;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]), acc_bar = smem_u32(&bars[8]);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int planes = p.planes;
   const uint32_t idesc = p.idesc;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -210,7 +215,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     mbar_init(acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TILE_N);
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -225,9 +230,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
         mbar_expect_tx(full0 + 8 * st, stage_bytes);
         const uint32_t dst = smem_base + st * stage_bytes;
         const int k = k_lo + s * SLAB_K;
-        for (int pl = 0; pl < p.planes; ++pl) {
+        for (int pl = 0; pl < planes; ++pl) {
           tma_load_3d(dst + pl * PLANE_TILE_BYTES, &map_a, full0 + 8 * st, k + p.a_k0, a_row, pl);
-          tma_load_3d(dst + (p.planes + pl) * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, k + p.b_k0, b_row, pl);
+          const uint32_t bdst = dst + planes * PLANE_TILE_BYTES + pl * B_TILE_BYTES;
+#pragma unroll
+          for (int h = 0; h < TN / TILE_M; ++h)  // the TMA box is 128 rows
+            tma_load_3d(bdst + h * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, k + p.b_k0, b_row + h * TILE_M, pl);
         }
       }
     }
@@ -241,8 +249,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_base = smem_base + st * stage_bytes;
-        const uint32_t b_base = a_base + p.planes * PLANE_TILE_BYTES;
-        issue_slab_any(planes, tmem_acc, a_base, b_base, idesc, accumulate);
+        const uint32_t b_base = a_base + planes * PLANE_TILE_BYTES;
+        if (TN == 128) issue_slab_any(planes, tmem_acc, a_base, b_base, idesc, accumulate);
+        else issue_slab<1>(tmem_acc, a_base, b_base, idesc, accumulate);
         umma_commit(empty0 + 8 * st);  // the stage is free once these MMAs have read it
       }
       umma_commit(acc_bar);  // arrives when every MMA issued above has completed
@@ -253,44 +262,52 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     float* __restrict__ C = p.C + (int64_t)b * p.c_bs;
     const int row = m0 + q * 32 + lane;
     const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-    // whole 32 x 128 quadrant in range: coalesced path (uniform in the warp, tcgen05.ld is warp-wide)
-    const bool whole = vec_ok && m0 + q * 32 + 32 <= p.M && n0 + TILE_N <= N;
+    // whole 32 x TN quadrant in range: coalesced path (uniform in the warp, tcgen05.ld is warp-wide)
+    const bool whole = vec_ok && m0 + q * 32 + 32 <= p.M && n0 + TN <= N;
     bool ok = true;
+    bool waited = false;
     if (whole) {
       // lane l handles row 4*it + l/8, columns 4*(l%8).. of each 32-column chunk: every global
-      // access of the warp is four full 128-byte row segments.  C is requested before the
-      // accumulator is waited for.
+      // access of the warp is four full 128-byte row segments.  The first 128 columns of C are
+      // requested before the accumulator is waited for.
       float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * p.ldc + n0 + (lane & 7) * 4;
-      float4 old[TILE_N / 4];
-      if (p.beta != 0.0f) {
+      // Symmetric result (p.mirror): the upper triangle is authoritative.  In units of 32 x 32
+      // blocks (gr, gc): gc > gr is stored and also stored transposed, gc == gr is symmetrised
+      // (A_i B_j and A_j B_i are summed in different orders by the MMA), gc < gr is left to the
+      // transposed store of its mirror block.  C[n,m] == C[m,n] then holds bit for bit.
+      const int gr = (m0 >> 5) + q;
+#pragma unroll 1
+      for (int half = 0; half < TN / 128 && ok; ++half) {
+        float4 old[32];
+        if (p.beta != 0.0f) {
 #pragma unroll
-        for (int c = 0; c < TILE_N / 32; ++c)
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int it = 0; it < 8; ++it) old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32);
-      }
-      if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
-      tc_fence_after();
-      // every MMA has completed, so the operand stages are free: stage 0 becomes the staging tiles
-      float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_LD;
-      // Symmetric result (p.mirror): the upper triangle is authoritative and every 32 x 32 block
-      // above the diagonal is also stored transposed.  A tile on the diagonal holds both halves
-      // from the MMA, but A_i B_j and A_j B_i are summed in different orders there, so its blocks
-      // below the diagonal are not stored and its diagonal blocks are symmetrised, which makes
-      // C[n,m] == C[m,n] bit for bit.
-      const bool diag_tile = p.mirror && n0 == m0;
-      if (ok) {
+            for (int it = 0; it < 8; ++it)
+              old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * p.ldc + half * 128 + c * 32);
+        }
+        if (!waited) {
+          if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
+          tc_fence_after();
+          waited = true;
+          if (!ok) break;
+        }
+        // every MMA has completed, so the operand stages are free: stage 0 becomes the staging tiles
+        float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_LD;
 #pragma unroll
-        for (int c = 0; c < TILE_N / 32; ++c) {
+        for (int c = 0; c < 4; ++c) {
           float v[32];
           if (have_acc) {
-            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128 + c * 32), v);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.0f;
           }
-          const bool store_direct = !(diag_tile && c <= q);
-          const bool store_mirror = p.mirror && (n0 > m0 || c > q);
-          const bool symmetrise = diag_tile && c == q;
+          const int gc = ((n0 + half * 128) >> 5) + c;
+          const bool store_direct = !p.mirror || gc > gr;
+          const bool store_mirror = p.mirror && gc > gr;
+          const bool symmetrise = p.mirror && gc == gr;
+          const int coff = half * 128 + c * 32;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -305,7 +322,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
               o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
               o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
             }
-            if (store_direct) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = o;
+            if (store_direct) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + coff) = o;
             if (p.mirror) *reinterpret_cast<float4*>(sp) = o;  // keep the final values for the stores below
           }
           __syncwarp();
@@ -316,12 +333,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
               float e[4];
 #pragma unroll
               for (int t = 0; t < 4; ++t) e[t] = (cc + t >= r) ? stage[r * STAGE_LD + cc + t] : stage[(cc + t) * STAGE_LD + r];
-              *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + c * 32) = make_float4(e[0], e[1], e[2], e[3]);
+              *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + coff) = make_float4(e[0], e[1], e[2], e[3]);
             }
           }
           if (store_mirror) {
-            // C[n0 + 32c + i][m0 + 32q + l] = final[l][i]: one 128-byte row segment per i
-            float* mq = C + (int64_t)(n0 + c * 32) * p.ldc + m0 + q * 32 + lane;
+            // C[n0 + coff + i][m0 + 32q + l] = final[l][i]: one 128-byte row segment per i
+            float* mq = C + (int64_t)(n0 + coff) * p.ldc + m0 + q * 32 + lane;
 #pragma unroll 8
             for (int i = 0; i < 32; ++i) mq[(int64_t)i * p.ldc] = stage[lane * STAGE_LD + i];
           }
@@ -333,7 +350,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
       tc_fence_after();
       if (ok) {
 #pragma unroll 1
-        for (int c = 0; c < TILE_N / 32; ++c) {
+        for (int c = 0; c < TN / 32; ++c) {
           float v[32];
           if (have_acc) {
             tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
@@ -349,7 +366,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
               if (col0 + j < N) {
                 float o = p.alpha * v[j];
                 if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
-                if (!(p.mirror && col0 + j < row)) dst[j] = o;   // symmetric result: the upper triangle is authoritative
+                // symmetric result: the upper triangle is authoritative; inside a diagonal 32 x 32
+                // block the coalesced path symmetrises, so take the element of the upper half there too
+                if (!(p.mirror && col0 + j < row)) dst[j] = o;
                 if (p.mirror && col0 + j > row) C[(int64_t)(col0 + j) * p.ldc + row] = o;
               }
             }
@@ -362,7 +381,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, TILE_N);
+    tmem_dealloc(tmem_acc, TN);
   }
 }
 
@@ -710,7 +729,8 @@ int configure_once() {
   int dev = 0;
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
-    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     done[dev & 63] = true;
   }
@@ -772,7 +792,15 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + STAGE_BYTES;  // A: two slabs, B: two stages, staging
     umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, p, run);
   } else {
-    umma_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
+    if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
+      // one product per element: 128 x 256 tiles, four 48 KB stages
+      p.stages = 4;
+      p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+      dim3 wgrid((unsigned)ceil_div(d.N, 256), (unsigned)ceil_div(d.M, TILE_M), 1);
+      umma_gemm_kernel<256><<<wgrid, GEMM_THREADS, (size_t)4 * (PLANE_TILE_BYTES + 2 * PLANE_TILE_BYTES) + 1024, st>>>(map_a, map_b, p);
+    } else {
+      umma_gemm_kernel<128><<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
+    }
   }
   MQ_LAUNCH_CHECK();
   return MQ_OK;

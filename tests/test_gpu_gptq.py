@@ -184,3 +184,22 @@ def test_quantize_many_streams_match_sequential(cuda, precision):
     torch.cuda.synchronize()
     for (q1, s1, z1), (q2, s2, z2) in zip(seq, par):
         assert torch.equal(q1, q2) and torch.equal(s1, s2) and torch.equal(z1, z2)
+
+
+def test_conv_layer_goes_through_unfold(cuda, precision):
+    """Convolutions are handled like the reference does: inputs unfolded to patches
+    (src/gptq.py:87-96), weight flattened to (out, in*kh*kw)."""
+    g = torch.Generator().manual_seed(2)
+    conv = nn.Conv2d(8, 16, kernel_size=2, stride=1, padding=1, bias=False, dtype=torch.bfloat16)
+    conv.weight.data = (0.05 * torch.randn(16, 8, 2, 2, generator=g)).to(torch.bfloat16)
+    x = torch.randn(3, 8, 12, 12, generator=g).to(torch.bfloat16)
+    h = GPTQ(conv.to(cuda), 32, True, 1e-2, 128, precision=precision)
+    h.update(x.to(cuda))
+    q, s, z = h.quantize(4)
+    assert q.shape == (16, 32) and s.shape == (16, 1)
+    patches = nn.Unfold(2, dilation=1, padding=1, stride=1)(x.float()).transpose(1, 2).flatten(0, 1).to(torch.bfloat16)
+    assert h.tokens_collected == patches.shape[0]
+    H, _ = O.hessian_update(None, 0, patches)
+    want = O.quantize_layer(conv.weight.detach().cpu().flatten(1), H, bits=4, group_size=32, rel_damp=1e-2, block_size=128)
+    assert torch.equal(s.cpu().float(), want["scale"].float())
+    assert O.code_agreement(q.cpu(), want["qweight"]) >= 0.99

@@ -154,42 +154,49 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
   tblk += (int64_t)b * t_bs;
   rows += (int64_t)b * r_bs;
   {
-    // 16 independent float4 loads per thread are issued before any is used (one memory
-    // latency for the whole 64 KB block instead of one per element)
+    // 16 independent float4 loads per thread plus the diagonal are issued before any is used (one
+    // memory latency for the whole 64 KB block).  float4 index: row j = idx % 128, columns
+    // k4..k4+3; consecutive threads take consecutive rows so that the transposed shared-memory
+    // stores hit 32 different banks.
     float4 v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const int idx = threadIdx.x + i * 256;     // float4 index: row j, columns k4..k4+3
-      const int j = idx >> 5, k4 = (idx & 31) * 4;
+      const int idx = threadIdx.x + i * 256;
+      const int j = idx & 127, k4 = (idx >> 7) * 4;
       v[i] = (j < nb && k4 < nb) ? __ldg(reinterpret_cast<const float4*>(tblk + (int64_t)j * ldt + k4))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    if (threadIdx.x < NB) {
+      const int k = threadIdx.x;
+      const float d = k < nb ? __ldg(tblk + (int64_t)k * ldt + k) : 1.0f;
+      dg[k] = d;
+      rdg[k] = 1.0f / d;
+    }
+    __syncthreads();
+    // The block is staged with every column already divided by its diagonal entry
+    // (TT[k][j] = T[j][k] / T[k][k], zero for j >= k), so a substitution step is
+    // a_j -= a_k * TT[k][j]: no division and no write-back of a_k inside the chain; the quotients
+    // p_k = a_k / T[k][k] are formed once at the end.
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int idx = threadIdx.x + i * 256;
-      const int j = idx >> 5, k4 = (idx & 31) * 4;
-      const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      const int j = idx & 127, k4 = (idx >> 7) * 4;
+      const float4 r4 = *reinterpret_cast<const float4*>(&rdg[k4]);
+      const float e[4] = {v[i].x * r4.x, v[i].y * r4.y, v[i].z * r4.z, v[i].w * r4.w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int k = k4 + q;
-        const float val = (j < nb && k < nb) ? e[q] : (j == k ? 1.0f : 0.0f);
-        TT[k * TT_LD + j] = (j < k) ? val : 0.0f;
-        if (j == k) {
-          dg[k] = val;
-          rdg[k] = 1.0f / val;
-        }
-      }
+      for (int q = 0; q < 4; ++q) TT[(k4 + q) * TT_LD + j] = (j < k4 + q && k4 + q < nb) ? e[q] : 0.0f;
     }
   }
-  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
-  // Two rows per warp at a time: their substitution chains are independent, so one hides the
-  // shuffle and FMA latency of the other.
-  for (int r0 = 2 * (blockIdx.x * warps_per_block + (threadIdx.x >> 5)); r0 < nrows; r0 += 2 * gridDim.x * warps_per_block) {
-    float a[2][4];
+  // Four rows per warp at a time share each shared-memory read of TT and give the scheduler four
+  // independent shuffle/FMA chains.
+  constexpr int ROWS = 4;
+  __syncthreads();
+  for (int r0 = ROWS * (blockIdx.x * warps_per_block + (threadIdx.x >> 5)); r0 < nrows; r0 += ROWS * gridDim.x * warps_per_block) {
+    float a[ROWS][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < ROWS; ++h) {
       const int r = r0 + h;
       if (IDENTITY) {
 #pragma unroll
@@ -204,27 +211,34 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
     for (int kq = (nb >> 2) - 1; kq >= 0; --kq) {
 #pragma unroll
       for (int kk = 3; kk >= 0; --kk) {
-        const int k = kq * 4 + kk;
-        const float d = dg[k], rd = rdg[k];
-        const float4 tt = *reinterpret_cast<const float4*>(&TT[k * TT_LD + lane * 4]);
+        const float4 tt = *reinterpret_cast<const float4*>(&TT[(kq * 4 + kk) * TT_LD + lane * 4]);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          // a / d through the reciprocal and one correction step (the quotient refinement of a
-          // correctly rounded division), a few FMAs instead of the full division sequence
-          float p = a[h][kk] * rd;
-          p = fmaf(fmaf(-d, p, a[h][kk]), rd, p);
-          p = __shfl_sync(0xffffffffu, p, kq);
-          a[h][0] = fmaf(-p, tt.x, a[h][0]);
-          a[h][1] = fmaf(-p, tt.y, a[h][1]);
-          a[h][2] = fmaf(-p, tt.z, a[h][2]);
-          a[h][3] = fmaf(-p, tt.w, a[h][3]);
-          if (lane == kq) a[h][kk] = p;
+        for (int h = 0; h < ROWS; ++h) {
+          const float ak = __shfl_sync(0xffffffffu, a[h][kk], kq);
+          a[h][0] = fmaf(-ak, tt.x, a[h][0]);
+          a[h][1] = fmaf(-ak, tt.y, a[h][1]);
+          a[h][2] = fmaf(-ak, tt.z, a[h][2]);
+          a[h][3] = fmaf(-ak, tt.w, a[h][3]);
         }
       }
     }
+    {
+      const float4 d4 = *reinterpret_cast<const float4*>(&dg[lane * 4]);
+      const float4 r4 = *reinterpret_cast<const float4*>(&rdg[lane * 4]);
+      const float dd[4] = {d4.x, d4.y, d4.z, d4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+      for (int h = 0; h < ROWS; ++h)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          // a / d through the reciprocal and one correction step (the last stage of a correctly
+          // rounded division)
+          float pq = a[h][q] * rr[q];
+          a[h][q] = fmaf(fmaf(-dd[q], pq, a[h][q]), rr[q], pq);
+        }
+    }
     if (lane * 4 < nb) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < ROWS; ++h) {
         const int r = r0 + h;
         if (r >= nrows) continue;
         if (IDENTITY) {
@@ -239,7 +253,7 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
     if (!IDENTITY && planes) {
       // the trailing update reads this panel as bf16 planes (row, k = column inside the panel)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < ROWS; ++h) {
         const int r = r0 + h;
         if (r >= nrows) continue;
         uint16_t hi[4], mi[4], lo[4];
@@ -338,7 +352,7 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
     }
     MQ_LAUNCH_CHECK();
     if (k1 == 0) break;
-    int grid = (int)(ceil_div(k1, 16) < 148 * 2 ? ceil_div(k1, 16) : 148 * 2);
+    int grid = (int)(ceil_div(k1, 32) < 148 * 2 ? ceil_div(k1, 32) : 148 * 2);
     {
       ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
       trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0,
@@ -380,7 +394,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   const int P = (int)ceil_div(C, NB);
   // ---- inverse of the unit factor: invert the diagonal blocks, then merge pairs of blocks
   MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
-  trsm_rows_kernel<true><<<dim3(8, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
+  trsm_rows_kernel<true><<<dim3(4, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
                                                              (int64_t)NB * (ldu + 1), NB, NB, (int)C, nullptr, 0, 0);
   MQ_LAUNCH_CHECK();
   for (int64_t s = NB; s < C; s *= 2) {

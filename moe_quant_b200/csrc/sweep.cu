@@ -59,11 +59,21 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
   if (have) {
     float4 v = *reinterpret_cast<const float4*>(W + (int64_t)r * ldw + c0);
     w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    const int grp = (int)group;
+    if ((grp & 3) == 0) {
+      // the four columns of a lane share a group: one index, one 32-bit division
+      const int64_t off = (int64_t)r * s_rs + (int64_t)(c0 / grp) * s_gs;
+      const float s0 = __ldg(scale + off);
+      const float z0 = zero ? __ldg(zero + off) : zero_default;
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      int64_t off = (int64_t)r * s_rs + ((c0 + t) / group) * s_gs;
-      sc[t] = __ldg(scale + off);
-      if (zero) zr[t] = __ldg(zero + off);
+      for (int t = 0; t < 4; ++t) { sc[t] = s0; zr[t] = z0; }
+    } else {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int64_t off = (int64_t)r * s_rs + (int64_t)((c0 + t) / grp) * s_gs;
+        sc[t] = __ldg(scale + off);
+        if (zero) zr[t] = __ldg(zero + off);
+      }
     }
   }
   float qv[4] = {0.f, 0.f, 0.f, 0.f}, yv[4] = {0.f, 0.f, 0.f, 0.f}, ev[4] = {0.f, 0.f, 0.f, 0.f};

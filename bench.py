@@ -230,6 +230,46 @@ def run_b200(args):
     issues = sum(h.has_hessian_issues() for h in handles)
     fault = _lib.engine_fault()
     del handles, results
+
+    # ---- gate_proj + up_proj of an expert share their input, hence their Hessian: quantized as a
+    # tied pair they share one factorisation (quant.py --tie_gptq_handles; the reference factors twice)
+    from moe_quant_b200 import quantize_tied
+    n_pairs = max(2, steps // 4)
+    pair_pool = [torch.cuda.Stream(device=dev) for _ in range(min(n_streams, n_pairs))]
+
+    def make_pairs(n):
+        out = []
+        for i in range(n):
+            gate = make_handles(1)[0]
+            gate.layer.weight = nn.Parameter(weights[i % n_experts], requires_grad=False)
+            gate.H = hessians[i % n_experts].clone()
+            up_layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
+            up_layer.weight = nn.Parameter(weights[(i + 1) % n_experts], requires_grad=False)
+            out.append((gate, GPTQ(up_layer, GROUP, True, 1e-2, 128, tied_gptq_handle=gate)))
+        return out
+
+    def run_pairs(pairs):
+        cur = torch.cuda.current_stream(dev)
+        for st in pair_pool:
+            st.wait_stream(cur)
+        res = []
+        for i, (g_h, u_h) in enumerate(pairs):
+            with torch.cuda.stream(pair_pool[i % len(pair_pool)]):
+                res.append(quantize_tied([g_h, u_h], BITS))
+        for st in pair_pool:
+            cur.wait_stream(st)
+        return res
+
+    run_pairs(make_pairs(len(pair_pool)))
+    pairs = make_pairs(n_pairs)
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    pair_results = run_pairs(pairs)
+    p1.record()
+    barrier()
+    tied_layers_per_s = 2 * n_pairs / (p0.elapsed_time(p1) / 1e3)
+    del pairs, pair_results
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -345,7 +385,8 @@ def run_b200(args):
             "config": {"workload": WORKLOAD, "experts_rotated": n_experts, "tokens_per_expert": tokens,
                        "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
                        "parallelism": f"ep{world}", "streams": n_streams,
-                       "single_stream_layers_per_s_per_gpu": steps / (ms_single / 1e3), "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
+                       "single_stream_layers_per_s_per_gpu": steps / (ms_single / 1e3),
+                       "tied_gate_up_layers_per_s_per_gpu": tied_layers_per_s, "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
             "roofline": roofline, "kernel_time_shares": shares,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "layers/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -205,6 +205,9 @@ def run_b200(args):
     # ---- timed region: K quantize() calls, issued round-robin on `streams` CUDA streams
     # (independent experts: their kernel chains overlap on the GPU)
     n_streams = max(1, args.streams)
+    # every stream of the pool gets a warm-up layer: a stream's first layer allocates its
+    # workspace and its allocator pool, which synchronises the device
+    warmup = max(warmup, n_streams)
     handles = make_handles(warmup + steps)
     quantize_many(handles[:warmup], BITS, streams=n_streams)
     barrier()

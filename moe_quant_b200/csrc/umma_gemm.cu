@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded; a wait that expires records a code in g_engine_fault,
 // the kernel still frees its TMEM and returns.
 #include <cuda.h>
+#include <cstring>
 
 #include "engine.cuh"
 #include "profile.cuh"
@@ -48,6 +49,7 @@ struct UmmaParams {
   int planes, nterms, stages;
   uint32_t idesc;
   int mirror;  // symmetric result: every block above the diagonal is also stored transposed
+  int c_tma;   // panel kernel epilogue: 0 = loads/stores by the warps, 1 = TMA store (beta == 0), 2 = TMA add (beta == 1)
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -91,6 +93,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Epilogue through the TMA unit: a 32 x 32 fp32 box leaves shared memory as one bulk tensor
+// store, or as an element-wise fp32 add performed at the L2 (C += box) so that the SM never
+// reads C.  Completion is tracked with bulk async-groups of the issuing thread.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -401,6 +418,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b,
+                                                                  const __grid_constant__ CUtensorMap map_c,
                                                                   const UmmaParams p, const int run) {
   const int m0 = blockIdx.y * TILE_M;
   const int n_tiles = (p.N + TILE_N - 1) / TILE_N;
@@ -504,6 +522,52 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
     float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + 4u * (uint32_t)p.planes * PLANE_TILE_BYTES) +
                    (warp - 2) * 32 * STAGE_LD;
     bool ok = true;
+    if (p.c_tma) {
+      // Each warp owns two 4 KB boxes (32 rows x 128 B, 128-byte swizzle: no bank conflicts
+      // when every lane writes its own row).  Box b is rewritten only after the bulk
+      // operation issued from it two chunks earlier has read it.
+      const uint32_t box0 = smem_base + 4u * (uint32_t)planes * PLANE_TILE_BYTES + (uint32_t)(warp - 2) * 8192u;
+      const uint32_t my_row = box0 + (uint32_t)lane * 128u;
+      const int y = m0 + q * 32;
+      int chunk = 0;
+      for (int i = 0; i < count && ok; ++i) {
+        const int acc = i & 1;
+        const int n0 = (nt_begin + i) * TILE_N;
+        ok = mbar_wait(acc_full + 8 * acc, (i >> 1) & 1, 15);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c, ++chunk) {
+          float v[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+          if (c == TILE_N / 32 - 1) {
+            // the accumulator is in registers: hand its TMEM columns back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+          }
+          if (lane == 0) bulk_wait_read_1();
+          __syncwarp();
+          const uint32_t dst = my_row + (uint32_t)(chunk & 1) * 4096u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((j ^ (lane & 7)) << 4)),
+                         "f"(p.alpha * v[4 * j]), "f"(p.alpha * v[4 * j + 1]), "f"(p.alpha * v[4 * j + 2]),
+                         "f"(p.alpha * v[4 * j + 3])
+                         : "memory");
+          fence_async_smem();
+          __syncwarp();
+          const int x = n0 + c * 32;
+          if (lane == 0 && y < p.M && x < p.N) {
+            if (p.c_tma == 2) tma_add_2d(&map_c, box0 + (uint32_t)(chunk & 1) * 4096u, x, y);
+            else tma_store_2d(&map_c, box0 + (uint32_t)(chunk & 1) * 4096u, x, y);
+          }
+          if (lane == 0) bulk_commit();
+        }
+      }
+      if (lane == 0) bulk_wait_read_all();  // the boxes have left shared memory; the writes land before the grid completes
+      __syncwarp();
+    } else
     for (int i = 0; i < count && ok; ++i) {
       const int acc = i & 1;
       const int n0 = (nt_begin + i) * TILE_N;
@@ -685,6 +749,21 @@ int encode_map(const PlaneSet& ps, CUtensorMap* map) {
   return MQ_OK;
 }
 
+// fp32 matrix C (M x N, row stride ldc) as a 2-D map with 32 x 32 boxes for the TMA epilogue.
+int encode_c_map(float* C, int64_t ldc, int M, int N, CUtensorMap* map) {
+  EncodeTiledFn enc;
+  MQ_TRY(get_encoder(&enc));
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MQ_REQUIRE(r == CUDA_SUCCESS, MQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d for C (M=%d N=%d ldc=%lld)", (int)r, M, N,
+             (long long)ldc);
+  return MQ_OK;
+}
+
 int pad_to(int x, int a) { return (x + a - 1) / a * a; }
 
 template <typename TIn, typename TPlane>
@@ -731,7 +810,7 @@ int configure_once() {
   if (!done[dev & 63]) {
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -787,10 +866,22 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
         if (cost < best) { best = cost; run = cand; }
       }
     }
-    (void)tiles;
     dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);
-    const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + STAGE_BYTES;  // A: two slabs, B: two stages, staging
-    umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, p, run);
+    // C goes through the TMA unit when the map can be built (16-byte aligned rows, and a beta
+    // that a plain store (0) or an add at the L2 (1) expresses) and every SM has at least two
+    // tiles: with fewer, the warps' own prefetched read-modify-write has the shorter latency.
+    // N must be a multiple of 4: the unit clips a box at the tensor's edge in 16-byte units,
+    // so a ragged last column would spill up to three elements past C's row.
+    CUtensorMap map_c;
+    memset(&map_c, 0, sizeof(map_c));
+    p.c_tma = 0;
+    if (tiles >= 2 * 148 && (d.ldc & 3) == 0 && (d.N & 3) == 0 && (reinterpret_cast<uintptr_t>(d.C) & 15) == 0 && (d.beta == 0.0f || d.beta == 1.0f)) {
+      MQ_TRY(encode_c_map(d.C, d.ldc, d.M, d.N, &map_c));
+      p.c_tma = d.beta == 0.0f ? 1 : 2;
+    }
+    const size_t staging = p.c_tma ? (size_t)4 * 2 * 4096 : (size_t)STAGE_BYTES;
+    const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + staging;  // A: two slabs, B: two stages, staging
+    umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, map_c, p, run);
   } else {
     if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
       // one product per element: 128 x 256 tiles, four 48 KB stages

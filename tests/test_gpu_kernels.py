@@ -289,6 +289,38 @@ def test_gemm_engine_upper_tiles_only(cuda, precision):
     assert torch.equal(got[~upper], C0.double()[~upper]), "tiles below the diagonal must not be touched"
 
 
+@pytest.mark.parametrize("beta", [0.0, 1.0, 0.5])
+@pytest.mark.parametrize("upper,N", [(False, 2780), (False, 2777), (True, 3304)])
+def test_gemm_engine_rank128_update_many_tiles(cuda, beta, upper, N):
+    """Rank-128 updates with at least two tiles per SM leave through the TMA unit (store for
+    beta 0, add at the L2 for beta 1); any other beta, or fewer tiles, goes through the warps'
+    own loads and stores, and so does an N that is not a multiple of 4.  Ragged edges (M, N not
+    multiples of the 32-wide boxes) and a C that is a window of a wider matrix must not touch
+    anything outside the window."""
+    M, K = (N, 128) if upper else (2500, 100)
+    g = torch.Generator().manual_seed(11)
+    A, B = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
+    if upper:
+        B = A.t().clone()
+    big = torch.randn(M + 3, (N + 43) // 4 * 4, generator=g)   # row stride is a multiple of 4 floats
+    big_d = big.clone().to(cuda)
+    Cd = big_d[2:2 + M, 8:8 + N]                      # 16-byte aligned window of a wider matrix
+    ops.gemm(A.to(cuda), B.to(cuda), Cd, alpha=-1.0, beta=beta, upper_tiles_only=upper,
+             precision=ops.Precision(math=MATH_TENSOR))
+    want = beta * big[2:2 + M, 8:8 + N].double() - A.double() @ B.double()
+    got = big_d.cpu()
+    win = got[2:2 + M, 8:8 + N].double()
+    mask = torch.ones(M, N, dtype=torch.bool)
+    if upper:
+        blocks_m, blocks_n = torch.arange(M) // 128, torch.arange(N) // 128
+        mask = blocks_m[:, None] <= blocks_n[None, :]
+        assert torch.equal(win[~mask], big[2:2 + M, 8:8 + N].double()[~mask])
+    assert float((win - want)[mask].abs().max() / want.abs().max()) < 5e-6
+    outside = torch.ones_like(big, dtype=torch.bool)
+    outside[2:2 + M, 8:8 + N] = False
+    assert torch.equal(got[outside], big[outside]), "elements outside the C window were modified"
+
+
 # ------------------------------------------------------------------ inverse-free form of the sweep
 def test_unit_factor_is_inverse_of_reference_factor(cuda, golden, precision):
     H = golden.t("H_damped").clone().to(cuda)

@@ -2,6 +2,7 @@
 """GPTQ layers/sec on the DeepSeek-V3 routed-expert gate_proj shape (2048 x 7168, 4 bit, g128).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --single-layer --steps 1        (small untimed case for profiler captures)
 
 One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1).  Routed experts
 are expert-parallel: every rank quantizes its own experts and nothing crosses NVLink, so the
@@ -52,51 +53,68 @@ def _peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs, read through NVML
+    (the source nvidia-smi prints) from a thread of this process.  NVML is initialised when the
+    sampler is built, long before the timed region: starting nvidia-smi at that moment instead
+    stalled the GPU's launches for up to half a second now and then."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index: int):
-        self.index, self.proc = index, None
+    def __init__(self, index: int, period_s: float = 0.02):
+        import threading
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.samples, self.recording, self.period = [], False, period_s
+        self.nvml = self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            props = torch.cuda.get_device_properties(index)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(props.uuid)).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+            return
+        self._stop = threading.Event()
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _reasons(self) -> int:
+        fn = getattr(self.nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        return int(fn(self.handle))
+
+    def _loop(self):
+        while not self._stop.is_set():
+            if self.recording:
+                try:
+                    self.samples.append((float(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)),
+                                         self._reasons()))
+                except Exception:
+                    pass
+            self._stop.wait(self.period)
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        self.samples, self.recording = [], True
         return self
 
     def __exit__(self, *exc):
-        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        self.recording = False
+        if self.nvml is None or not self.samples:
             return
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 8:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for n, v in zip(names, f[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if sm:
-            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                           "samples": len(sm)}
+        mask = 0
+        for _, r in self.samples:
+            mask |= r
+        self.result = {"sm_mhz": statistics.median(c for c, _ in self.samples), "sm_max_mhz": self.max_mhz,
+                       "reasons": sorted(n for bit, n in self.REASONS.items() if mask & bit), "samples": len(self.samples)}
+
+    def close(self):
+        if self.nvml is not None:
+            self._stop.set()
+            self.thread.join(timeout=1)
 
 
 def _dist():
@@ -166,6 +184,7 @@ def run_b200(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     steps, warmup = args.steps, max(args.warmup, 3)
+    clocks = ClockSampler(local)         # NVML comes up here, not beside the timed region
     n_experts = 4
     seed = 1234 + 100 * rank
 
@@ -205,22 +224,33 @@ def run_b200(args):
     # ---- timed region: K quantize() calls, issued round-robin on `streams` CUDA streams
     # (independent experts: their kernel chains overlap on the GPU)
     n_streams = max(1, args.streams)
-    # every stream of the pool gets a warm-up layer: a stream's first layer allocates its
-    # workspace and its allocator pool, which synchronises the device
-    warmup = max(warmup, n_streams)
-    handles = make_handles(warmup + steps)
-    quantize_many(handles[:warmup], BITS, streams=n_streams)
+    # The warm-up is a whole pass of the same length with its results kept, then dropped: every
+    # stream of the pool gets its workspace, and the caching allocator's per-stream pools hold
+    # every block the timed pass will ask for.  A cudaMalloc inside the timed region goes
+    # through the driver's global lock, which other jobs on a shared host can hold for tens of
+    # milliseconds at a time.
+    warmup = max(warmup, steps)
+    pre = make_handles(warmup)
+    pre_results = quantize_many(pre, BITS, streams=n_streams)
+    barrier()
+    del pre, pre_results
+    handles = make_handles(steps)
     barrier()
     launches0 = _lib.lib().mq_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with clocks:
         ev0.record()
-        results = quantize_many(handles[warmup:], BITS, streams=n_streams)
+        results = quantize_many(handles, BITS, streams=n_streams)
         ev1.record()
         barrier()
+    clocks.close()
     ms_total = ev0.elapsed_time(ev1)
     launches = _lib.lib().mq_launch_count() - launches0
     # the same K calls one after the other on one stream (what a plain `for handle: quantize` loop gets)
+    seq_pre = make_handles(steps)          # same untimed pass first, for the same reason
+    seq_pre_results = [h.quantize(BITS) for h in seq_pre]
+    barrier()
+    del seq_pre, seq_pre_results
     seq_handles = make_handles(steps)
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -263,7 +293,9 @@ def run_b200(args):
             cur.wait_stream(st)
         return res
 
-    run_pairs(make_pairs(len(pair_pool)))
+    pre_pairs = run_pairs(make_pairs(n_pairs))
+    barrier()
+    del pre_pairs
     pairs = make_pairs(n_pairs)
     barrier()
     p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -296,13 +328,21 @@ def run_b200(args):
         shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
         v = kinds[top]
         if top in ("umma_gemm", "simt_gemm"):
-            achieved = v["work"] / (v["ms"] / 1e3) / 1e12
+            secs = v["ms"] / 1e3
+            products = 6.0 if top == "umma_gemm" else 1.0     # bf16 products per fp32 product with three planes
+            achieved = v["work"] * products / secs / 1e12
+            # DRAM bytes per 128x128 output tile of a rank-128 update from the committed ncu capture
+            # (141.1 MB for 1485 tiles, profiles/umma_panel_kernel_trailing_update_7168.md); traffic
+            # grows with the tile count, so the average launch is scaled by its tiles
+            tiles_per_launch = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
             roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
-                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"], "traffic": None,
-                        "issued_tflops": v["work2"] / (v["ms"] / 1e3) / 1e12,
-                        "frac_issued": v["work2"] / (v["ms"] / 1e3) / 1e12 / peaks["tensor_sustained"],
-                        "note": "achieved counts fp32-equivalent flop (2MNK on kept tiles); every fp32 product is "
-                                "six bf16 tensor products (3 planes), which is what issued_tflops / frac_issued count",
+                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
+                        "traffic": 95.0e3 * tiles_per_launch if top == "umma_gemm" else None,
+                        "traffic_note": "bytes per average launch, scaled by tiles from an ncu capture of two large launches",
+                        "fp32_equivalent_tflops": v["work"] / secs / 1e12,
+                        "padded_tflops": v["work2"] / secs / 1e12,
+                        "note": "algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products "
+                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once",
                         "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
                         "peak_source": peaks["source"] + " (sustained bf16)"}
         else:
@@ -361,7 +401,7 @@ def run_b200(args):
             cur.wait_stream(st)
 
     e2e_steps = steps
-    e2e_run(max(warmup, n_streams))
+    e2e_run(max(e2e_steps, n_streams))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -404,6 +444,25 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_single_layer(args):
+    """The small case for profiler captures: one Hessian from 4096 bf16 tokens, one 2048 x 7168
+    layer quantized `--steps` times on one stream (about 1 GB on the device), no timing."""
+    from moe_quant_b200 import _lib, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    W = (0.02 * torch.randn(R, C, generator=g, device=dev)).to(torch.bfloat16)
+    chan = torch.exp(torch.randn(C, generator=g, device=dev))
+    X = (torch.randn(TOKENS, C, generator=g, device=dev) * chan).to(torch.bfloat16)
+    H = torch.zeros(C, C, device=dev)
+    ops.hessian_accum(H, X, 0.0, 2.0 / TOKENS)
+    for _ in range(max(1, args.steps)):
+        ops.quantize_layer([W], H.clone(), GROUP, BITS, 1e-2)
+    torch.cuda.synchronize()
+    print(json.dumps({"single_layer": True, "launches": int(_lib.lib().mq_launch_count()),
+                      "engine_fault": int(_lib.engine_fault())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,8 +471,12 @@ def main():
     ap.add_argument("--streams", type=int, default=8, help="CUDA streams the independent layers are spread over")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--single-layer", action="store_true",
+                    help="run one Hessian accumulation and --steps layers untimed (profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single_layer:
+        run_single_layer(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

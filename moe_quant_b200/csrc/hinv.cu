@@ -31,83 +31,122 @@ constexpr int NB = 128;  // panel width
 
 // ------------------------------------------------------------------ diagonal block
 // D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
-// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers.  The 128 pivots are
-// taken 8 at a time: the thread that owns diagonal tile kt factors it alone in registers
-// (no barrier inside), the 8-wide panel above it is solved by the threads of tile column
-// kt, and every remaining upper tile takes one rank-8 update.  Three barriers per 8 pivots.
+// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers, and the 16 threads
+// of one tile column are the 16 lanes of a half-warp.  The 128 pivots are taken 8 at a time.
+// For leaf kt the half-warp of tile column kt works alone: the owner of the diagonal tile
+// publishes it, every lane factors its own copy in registers (the same arithmetic 16 times,
+// no communication inside the chain of 8 pivots) and applies each pivot to its 8 rows of the
+// panel above the leaf as soon as it exists, so the panel solve fills the latency gaps of the
+// pivot chain.  One block-wide barrier per leaf; then every remaining upper tile takes one
+// rank-8 update from the panel, which is double buffered so that the next leaf's half-warp
+// may write its panel while slower warps still read this one.
 constexpr int PAN_LD = NB + 4;
 
 __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                             int k_global, mq_layer_flags* flags) {
-  __shared__ __align__(16) float pan[8][PAN_LD];  // pan[kk][row]: column 8kt+kk of T, rows above the leaf
-  __shared__ float leaf[8][8];                    // leaf[j][kk] = T[8kt+j][8kt+kk]
-  __shared__ float rdiag[8];                      // 1 / T[8kt+kk][8kt+kk]
+  __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of T, rows above the leaf
+  __shared__ __align__(16) float leaf_pub[8][8];     // the diagonal tile before its factorisation
   const int t = threadIdx.x;
-  const int tr = t >> 4, tc = t & 15;
+  const int warp = t >> 5, lane = t & 31;
+  const int tc = warp * 2 + (lane >> 4), tr = lane & 15;
   float a[8][8];
+  // Only tiles on or above the diagonal are ever read.  A whole, 16-byte aligned block moves
+  // as float4 (a quarter of the memory transactions of scalar accesses at this tile layout).
+  const bool vec = nb == NB && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(blk) & 15) == 0;
+  if (vec) {
+    if (tr <= tc) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      int r = tr * 8 + i, c = tc * 8 + j;
-      a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
-    }
-  for (int kt = 15; kt >= 0; --kt) {
-    if (tr == kt && tc == kt) {
-#pragma unroll
-      for (int kk = 7; kk >= 0; --kk) {
-        float d = a[kk][kk];
-        if (!(d > 0.0f)) {  // also catches NaN
-          if (kt * 8 + kk < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + kk + 1);
-          d = 1.0f;
-        }
-        float r = rsqrtf(d);
-        r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
-        a[kk][kk] = d * r;
-        rdiag[kk] = r;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (i < kk) a[i][kk] *= r;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (i <= j && j < kk) a[i][j] = fmaf(-a[i][kk], a[j][kk], a[i][j]);
+      for (int i = 0; i < 8; ++i) {
+        const float4 lo = *reinterpret_cast<const float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8);
+        const float4 hi = *reinterpret_cast<const float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8 + 4);
+        a[i][0] = lo.x; a[i][1] = lo.y; a[i][2] = lo.z; a[i][3] = lo.w;
+        a[i][4] = hi.x; a[i][5] = hi.y; a[i][6] = hi.z; a[i][7] = hi.w;
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) leaf[j][kk] = (j < kk) ? a[j][kk] : 0.0f;
     }
-    __syncthreads();
-    if (tc == kt && tr < kt) {
-      // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
+  } else {
 #pragma unroll
-      for (int kk = 7; kk >= 0; --kk) {
-        const float rd = rdiag[kk];
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int r = tr * 8 + i, c = tc * 8 + j;
+        a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
+      }
+  }
+  for (int kt = 15; kt >= 0; --kt) {
+    const int buf = kt & 1;
+    if (warp == (kt >> 1)) {
+      if (tc == kt && tr == kt) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float pv = a[i][kk] * rd;
-          a[i][kk] = pv;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (j < kk) a[i][j] = fmaf(-pv, leaf[j][kk], a[i][j]);
+          *reinterpret_cast<float4*>(&leaf_pub[i][0]) = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
+          *reinterpret_cast<float4*>(&leaf_pub[i][4]) = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
         }
       }
+      __syncwarp();
+      if (tc == kt && tr <= kt) {
+        float L[8][8];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        *reinterpret_cast<float4*>(&pan[kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-        *reinterpret_cast<float4*>(&pan[kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
+        for (int i = 0; i < 8; ++i) {
+          const float4 lo = *reinterpret_cast<const float4*>(&leaf_pub[i][0]);
+          const float4 hi = *reinterpret_cast<const float4*>(&leaf_pub[i][4]);
+          L[i][0] = lo.x; L[i][1] = lo.y; L[i][2] = lo.z; L[i][3] = lo.w;
+          L[i][4] = hi.x; L[i][5] = hi.y; L[i][6] = hi.z; L[i][7] = hi.w;
+        }
+        // The 8 pivots are one straight line of code (no branch), so that the scheduler can
+        // put the panel arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.
+        // The owner of the diagonal tile runs the panel arithmetic on its own tile too; that
+        // copy is discarded below.
+        int fail = 0;
+#pragma unroll
+        for (int kk = 7; kk >= 0; --kk) {
+          float d = L[kk][kk];
+          const bool bad = !(d > 0.0f);  // also catches NaN
+          fail = (bad && fail == 0) ? kk + 1 : fail;
+          d = bad ? 1.0f : d;
+          float r = rsqrtf(d);
+          r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
+          L[kk][kk] = d * r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < kk) L[i][kk] *= r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i <= j && j < kk) L[i][j] = fmaf(-L[i][kk], L[j][kk], L[i][j]);
+          // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float pv = a[i][kk] * r;
+            a[i][kk] = pv;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j < kk) a[i][j] = fmaf(-pv, L[j][kk], a[i][j]);
+          }
+        }
+        if (tr < kt) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
+            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
+          }
+        } else {
+          if (fail != 0 && kt * 8 + fail - 1 < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + fail);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[i][j] = (i <= j) ? L[i][j] : 0.0f;
+        }
       }
     }
     __syncthreads();
     if (tr <= tc && tc < kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const float4 i0 = *reinterpret_cast<const float4*>(&pan[kk][tr * 8]);
-        const float4 i1 = *reinterpret_cast<const float4*>(&pan[kk][tr * 8 + 4]);
-        const float4 j0 = *reinterpret_cast<const float4*>(&pan[kk][tc * 8]);
-        const float4 j1 = *reinterpret_cast<const float4*>(&pan[kk][tc * 8 + 4]);
+        const float4 i0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8]);
+        const float4 i1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8 + 4]);
+        const float4 j0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8]);
+        const float4 j1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8 + 4]);
         const float pi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
         const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
 #pragma unroll
@@ -117,13 +156,26 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
       }
     }
   }
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      int r = tr * 8 + i, c = tc * 8 + j;
-      if (r < nb && c < nb) blk[(int64_t)r * ld + c] = (r <= c) ? a[i][j] : 0.0f;
+    for (int i = 0; i < 8; ++i) {
+      float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+      if (tr <= tc) {  // the diagonal tiles were zeroed below their diagonal when they were factored
+        lo = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
+        hi = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
+      }
+      *reinterpret_cast<float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8) = lo;
+      *reinterpret_cast<float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8 + 4) = hi;
     }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int r = tr * 8 + i, c = tc * 8 + j;
+        if (r < nb && c < nb) blk[(int64_t)r * ld + c] = (r <= c) ? a[i][j] : 0.0f;
+      }
+  }
 }
 
 // ------------------------------------------------------------------ substitution

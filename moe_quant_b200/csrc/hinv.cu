@@ -334,7 +334,23 @@ __global__ void __launch_bounds__(256) extract_diag_kernel(const float* __restri
 // T -> T diag(T)^-1 on the upper triangle (unit diagonal), zeros below it.
 __global__ void __launch_bounds__(256) scale_columns_kernel(float* __restrict__ H, int64_t C, int64_t ld,
                                                             const float* __restrict__ diag) {
-  int64_t r = blockIdx.y;
+  const int64_t r = blockIdx.y;
+  if ((C & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) {
+    // four columns per thread; what lies entirely below the diagonal is written without being read
+    for (int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; c < C; c += (int64_t)gridDim.x * blockDim.x * 4) {
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c + 3 >= r) {
+        const float4 v = *reinterpret_cast<const float4*>(H + r * ld + c);
+        const float4 d = __ldg(reinterpret_cast<const float4*>(diag + c));
+        o.x = (c + 0 > r) ? v.x / d.x : (c + 0 == r ? 1.0f : 0.0f);
+        o.y = (c + 1 > r) ? v.y / d.y : (c + 1 == r ? 1.0f : 0.0f);
+        o.z = (c + 2 > r) ? v.z / d.z : (c + 2 == r ? 1.0f : 0.0f);
+        o.w = (c + 3 > r) ? v.w / d.w : (c + 3 == r ? 1.0f : 0.0f);
+      }
+      *reinterpret_cast<float4*>(H + r * ld + c) = o;
+    }
+    return;
+  }
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < C; c += (int64_t)gridDim.x * blockDim.x) {
     float v = H[r * ld + c];
     H[r * ld + c] = (c > r) ? v / diag[c] : (c == r ? 1.0f : 0.0f);

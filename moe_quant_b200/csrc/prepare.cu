@@ -9,16 +9,24 @@ namespace mq {
 // ---------------------------------------------------------------- NaN guard
 __global__ void __launch_bounds__(256) nan_scan_kernel(const float* __restrict__ H, int64_t C, int64_t ldh,
                                                        mq_layer_flags* flags) {
-  // C % 4 == 0 and ldh % 4 == 0 (checked on the host): rows are float4-addressable.
-  int64_t vec_per_row = C / 4;
-  int64_t n = C * vec_per_row;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // C % 4 == 0 and ldh % 4 == 0 (checked on the host): rows are float4-addressable.  A thread
+  // keeps its column and walks rows, four independent loads per step, no index division.
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   bool bad = false;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    int64_t r = i / vec_per_row;
-    int64_t c = (i - r * vec_per_row) * 4;
-    float4 v = __ldg(reinterpret_cast<const float4*>(H + r * ldh + c));
-    bad |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+  if (c < C) {
+    const float* col = H + c;
+    int64_t r = blockIdx.y;
+    for (; r + 3 * (int64_t)gridDim.y < C; r += 4 * (int64_t)gridDim.y) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldg(reinterpret_cast<const float4*>(col + (r + u * (int64_t)gridDim.y) * ldh));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) bad |= (v[u].x != v[u].x) | (v[u].y != v[u].y) | (v[u].z != v[u].z) | (v[u].w != v[u].w);
+    }
+    for (; r < C; r += gridDim.y) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(col + r * ldh));
+      bad |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+    }
   }
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch(&flags->nan_hessian, 1);
 }
@@ -201,8 +209,13 @@ extern "C" int mq_hessian_prepare(float* H, int64_t C, int64_t ldh, float* W, in
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   MQ_CUDA(cudaMemsetAsync(flags, 0, sizeof(mq_layer_flags), st));
-  int scan_grid = (int)(ceil_div(C * C / 4, 256) < 148 * 8 ? ceil_div(C * C / 4, 256) : 148 * 8);
-  nan_scan_kernel<<<scan_grid, 256, 0, st>>>(H, C, ldh, flags);
+  {
+    const unsigned gx = (unsigned)ceil_div(C / 4, 256);
+    unsigned gy = (unsigned)(148 * 8 / gx);
+    if (gy < 1) gy = 1;
+    if ((int64_t)gy > C) gy = (unsigned)C;
+    nan_scan_kernel<<<dim3(gx, gy), 256, 0, st>>>(H, C, ldh, flags);
+  }
   MQ_LAUNCH_CHECK();
   identity_if_nan_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags);
   MQ_LAUNCH_CHECK();

@@ -206,8 +206,9 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
   tblk += (int64_t)b * t_bs;
   rows += (int64_t)b * r_bs;
   {
-    // 16 independent float4 loads per thread plus the diagonal are issued before any is used (one
-    // memory latency for the whole 64 KB block).  float4 index: row j = idx % 128, columns
+    // Up to 16 independent float4 loads per thread plus the diagonal are issued before any is used
+    // (one memory latency for the block); quads that lie below the diagonal are zeros in the
+    // staged form and are not loaded.  float4 index: row j = idx % 128, columns
     // k4..k4+3; consecutive threads take consecutive rows so that the transposed shared-memory
     // stores hit 32 different banks.
     float4 v[16];
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
     for (int i = 0; i < 16; ++i) {
       const int idx = threadIdx.x + i * 256;
       const int j = idx & 127, k4 = (idx >> 7) * 4;
-      v[i] = (j < nb && k4 < nb) ? __ldg(reinterpret_cast<const float4*>(tblk + (int64_t)j * ldt + k4))
+      v[i] = (j < nb && k4 < nb && k4 + 3 > j) ? __ldg(reinterpret_cast<const float4*>(tblk + (int64_t)j * ldt + k4))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (threadIdx.x < NB) {

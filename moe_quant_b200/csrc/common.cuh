@@ -4,6 +4,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -37,6 +38,32 @@ extern long long g_launches;  // kernels launched by this library in this proces
     ++mq::g_launches;             \
     MQ_CUDA(cudaGetLastError());  \
   } while (0)
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// The kernels of the layer loop (diagonal block, panel solve, rank-128 update, sweep tile) are
+// a chain of small dependent launches.  Launched through launch_chained, a kernel may be
+// made resident while its predecessor in the stream still runs; it must call
+// chain_wait() before it touches global memory (that returns once every earlier grid has
+// completed and its writes are visible) and then chain_release(), which lets its own successor
+// be made resident.  Releasing only after the wait keeps at most one waiting grid on the GPU.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
 
 #define MQ_TRY(expr)              \
   do {                            \

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
                                                             int k_global, mq_layer_flags* flags) {
   __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of T, rows above the leaf
   __shared__ __align__(16) float leaf_pub[8][8];     // the diagonal tile before its factorisation
+  chain_wait();
+  chain_release();
   const int t = threadIdx.x;
   const int warp = t >> 5, lane = t & 31;
   const int tc = warp * 2 + (lane >> 4), tr = lane & 15;
@@ -193,6 +195,8 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
                                                         int nrows, int nb_full, int n_total,
                                                         uint16_t* __restrict__ planes, int64_t plane_stride, int n_planes) {
   extern __shared__ __align__(16) float smem[];
+  chain_wait();
+  chain_release();
   float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
   float* dg = smem + NB * TT_LD;   // [NB] diagonal of T
   float* rdg = dg + NB;            // [NB] its reciprocal
@@ -417,16 +421,15 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
     float* dblk = H + k1 * ldh + k1;
     {
       ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
-      chol_diag_rev_kernel<<<1, 256, 0, st>>>(dblk, ldh, nb, (int)k1, flags);
+      MQ_CUDA(launch_chained(chol_diag_rev_kernel, dim3(1), dim3(256), 0, st, dblk, ldh, nb, (int)k1, flags));
     }
     MQ_LAUNCH_CHECK();
     if (k1 == 0) break;
     int grid = (int)(ceil_div(k1, 32) < 148 * 2 ? ceil_div(k1, 32) : 148 * 2);
     {
       ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
-      trsm_rows_kernel<false><<<dim3(grid, 1), 256, kTrsmSmem, st>>>(dblk, ldh, 0, H + k1, ldh, 0, (int)k1, nb, 0,
-                                                                     tensor ? pset.base : nullptr,
-                                                                     tensor ? pset.total_rows * NB : 0, split);
+      MQ_CUDA(launch_chained(trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
+                             (int)k1, nb, 0, tensor ? pset.base : nullptr, tensor ? pset.total_rows * NB : 0, split));
     }
     MQ_LAUNCH_CHECK();
     GemmDesc g;

@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     int n_planes) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
+  chain_wait();
+  chain_release();
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
     int j = idx >> 5, k4 = (idx & 31) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -211,19 +213,19 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
     ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
     switch (out_dtype) {
       case MQ_F32:
-        sweep_tile_kernel<MQ_F32><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_F32>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<float*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       case MQ_BF16:
-        sweep_tile_kernel<MQ_BF16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_BF16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                    maxq, zero_default, codes, C,
-                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
+                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       default:
-        sweep_tile_kernel<MQ_F16><<<grid, SWEEP_THREADS, smem, st>>>(W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_F16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split);
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
     }
     }
     MQ_LAUNCH_CHECK();

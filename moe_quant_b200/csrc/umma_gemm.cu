@@ -459,6 +459,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = tmem_slot;
+  // barriers and tensor memory are set up; from here on global memory is touched
+  chain_wait();
+  chain_release();
 
   // Producer and MMA warps run their loops with all 32 lanes (every lane waits on the
   // barriers); one lane issues the TMA / tcgen05 instructions.
@@ -881,7 +884,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     }
     const size_t staging = p.c_tma ? (size_t)4 * 2 * 4096 : (size_t)STAGE_BYTES;
     const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + staging;  // A: two slabs, B: two stages, staging
-    umma_panel_kernel<<<pgrid, GEMM_THREADS, psmem, st>>>(map_a, map_b, map_c, p, run);
+    MQ_CUDA(launch_chained(umma_panel_kernel, pgrid, dim3(GEMM_THREADS), psmem, st, map_a, map_b, map_c, p, run));
   } else {
     if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
       // one product per element: 128 x 256 tiles, four 48 KB stages

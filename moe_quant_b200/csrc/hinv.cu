@@ -421,14 +421,14 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
     float* dblk = H + k1 * ldh + k1;
     {
       ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
-      MQ_CUDA(launch_chained(chol_diag_rev_kernel, dim3(1), dim3(256), 0, st, dblk, ldh, nb, (int)k1, flags));
+      MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(256), 0, st, dblk, ldh, nb, (int)k1, flags));
     }
     MQ_LAUNCH_CHECK();
     if (k1 == 0) break;
     int grid = (int)(ceil_div(k1, 32) < 148 * 2 ? ceil_div(k1, 32) : 148 * 2);
     {
       ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
-      MQ_CUDA(launch_chained(trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
+      MQ_CUDA(launch_chained(true, trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
                              (int)k1, nb, 0, tensor ? pset.base : nullptr, tensor ? pset.total_rows * NB : 0, split));
     }
     MQ_LAUNCH_CHECK();

@@ -34,8 +34,8 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     int n_planes) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
-  chain_wait();
-  chain_release();
+  // The factor is constant during the sweep: its tile is staged before this grid waits for the
+  // rank-128 update that precedes it in the stream (only W depends on that update).
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
     int j = idx >> 5, k4 = (idx & 31) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     }
     *reinterpret_cast<float4*>(&ublk[j * TILE + k4]) = v;
   }
+  chain_wait();
+  chain_release();
   __syncthreads();
 
   const int lane = threadIdx.x & 31;
@@ -210,20 +212,23 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
     const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
     // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
     {
+    // The kernel stages its tile of the factor before it waits for its predecessor: only a launch
+    // that follows this loop's own update (which writes W, never the factor) may be chained.
+    const bool chained = i1 > 0;
     ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
     switch (out_dtype) {
       case MQ_F32:
-        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_F32>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F32>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<float*>(deq), err,
                                                                   (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       case MQ_BF16:
-        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_BF16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_BF16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                    maxq, zero_default, codes, C,
                                                                    static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       default:
-        MQ_CUDA(launch_chained(sweep_tile_kernel<MQ_F16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
+        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
                                                                   (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
     }

@@ -884,7 +884,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     }
     const size_t staging = p.c_tma ? (size_t)4 * 2 * 4096 : (size_t)STAGE_BYTES;
     const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + staging;  // A: two slabs, B: two stages, staging
-    MQ_CUDA(launch_chained(umma_panel_kernel, pgrid, dim3(GEMM_THREADS), psmem, st, map_a, map_b, map_c, p, run));
+    MQ_CUDA(launch_chained(true, umma_panel_kernel, pgrid, dim3(GEMM_THREADS), psmem, st, map_a, map_b, map_c, p, run));
   } else {
     if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
       // one product per element: 128 x 256 tiles, four 48 KB stages

@@ -195,8 +195,6 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
                                                         int nrows, int nb_full, int n_total,
                                                         uint16_t* __restrict__ planes, int64_t plane_stride, int n_planes) {
   extern __shared__ __align__(16) float smem[];
-  chain_wait();
-  chain_release();
   float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
   float* dg = smem + NB * TT_LD;   // [NB] diagonal of T
   float* rdg = dg + NB;            // [NB] its reciprocal
@@ -209,6 +207,30 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
   }
   tblk += (int64_t)b * t_bs;
   rows += (int64_t)b * r_bs;
+  // Four rows per warp at a time share each shared-memory read of TT and give the scheduler four
+  // independent shuffle/FMA chains.
+  constexpr int ROWS = 4;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int r_first = ROWS * (blockIdx.x * warps_per_block + (threadIdx.x >> 5));
+  float a[ROWS][4];
+  // The rows of the panel were final before the diagonal block in front of this launch was
+  // factored (that kernel writes only the block), so the first rows are fetched before this grid
+  // waits for it; the block itself is staged after the wait.
+  if (!IDENTITY) {
+#pragma unroll
+    for (int h = 0; h < ROWS; ++h) {
+      const int r = r_first + h;
+      if (r < nrows && lane * 4 < nb) {
+        float4 v = *reinterpret_cast<const float4*>(rows + (int64_t)r * ldr + lane * 4);
+        a[h][0] = v.x; a[h][1] = v.y; a[h][2] = v.z; a[h][3] = v.w;
+      } else {
+        a[h][0] = a[h][1] = a[h][2] = a[h][3] = 0.0f;
+      }
+    }
+  }
+  chain_wait();
+  chain_release();
   {
     // Up to 16 independent float4 loads per thread plus the diagonal are issued before any is used
     // (one memory latency for the block); quads that lie below the diagonal are zeros in the
@@ -244,20 +266,16 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
       for (int q = 0; q < 4; ++q) TT[(k4 + q) * TT_LD + j] = (j < k4 + q && k4 + q < nb) ? e[q] : 0.0f;
     }
   }
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
-  // Four rows per warp at a time share each shared-memory read of TT and give the scheduler four
-  // independent shuffle/FMA chains.
-  constexpr int ROWS = 4;
   __syncthreads();
-  for (int r0 = ROWS * (blockIdx.x * warps_per_block + (threadIdx.x >> 5)); r0 < nrows; r0 += ROWS * gridDim.x * warps_per_block) {
-    float a[ROWS][4];
+  for (int r0 = r_first; r0 < nrows; r0 += ROWS * gridDim.x * warps_per_block) {
 #pragma unroll
     for (int h = 0; h < ROWS; ++h) {
       const int r = r0 + h;
       if (IDENTITY) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) a[h][q] = (lane * 4 + q == r) ? 1.0f : 0.0f;
+      } else if (r0 == r_first) {
+        // fetched before the wait
       } else if (r < nrows && lane * 4 < nb) {
         float4 v = *reinterpret_cast<const float4*>(rows + (int64_t)r * ldr + lane * 4);
         a[h][0] = v.x; a[h][1] = v.y; a[h][2] = v.z; a[h][3] = v.w;

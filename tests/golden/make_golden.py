@@ -143,4 +143,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python make_golden.py <path to a checkout of IST-DASLab/MoE-Quant>")
+    main(sys.argv[1])

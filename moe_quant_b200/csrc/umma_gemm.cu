@@ -33,7 +33,6 @@ namespace {
 constexpr int TILE_M = 128, TILE_N = 128, SLAB_K = 64;
 constexpr int PLANE_TILE_BYTES = TILE_M * SLAB_K * 2;  // 16 KB
 constexpr int GEMM_THREADS = 192;
-constexpr int MAX_TERMS = 6;
 constexpr int STAGE_LD = 36;                        // floats per row of an epilogue staging tile
 constexpr int STAGE_BYTES = 4 * 32 * STAGE_LD * 4;  // four epilogue warps
 
@@ -60,6 +59,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait: gives up after about one second and records `code`.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
@@ -108,6 +110,12 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -156,6 +164,31 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Matrix descriptor of an MN-major operand with the 128-byte swizzle, as a TMA box of
+// 64 (m or n, contiguous) x 64 (k) 16-bit elements lands in shared memory: one 128-byte row per
+// k, groups of 8 k 1024 bytes apart (stride byte offset), 64-wide blocks of m/n `block_bytes`
+// apart (leading byte offset).
+__device__ __forceinline__ uint64_t mnmajor_sw128_desc(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(block_bytes >> 4) << 16;  // leading byte offset
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+  d |= (uint64_t)1 << 46;                   // version
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+
+// One 64-wide K slab of a one-plane GEMM whose operands are MN-major boxes (8 KB per 64 rows of
+// m/n): a K step of 16 is two groups of 8 k, 2048 bytes.
+__device__ __forceinline__ void issue_slab_mn(uint32_t tmem_d, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+                                              uint32_t& accumulate) {
+  const uint64_t a0 = mnmajor_sw128_desc(a_tile, 8192), b0 = mnmajor_sw128_desc(b_tile, 8192);
+#pragma unroll
+  for (int kk = 0; kk < SLAB_K / 16; ++kk) {
+    umma_bf16(tmem_d, a0 + (uint64_t)((kk * 2048) >> 4), b0 + (uint64_t)((kk * 2048) >> 4), idesc, accumulate);
+    accumulate = 1;
+  }
+}
+
 // All MMAs of one 64-wide K slab: for each of the four K16 steps, the products A_i B_j with
 // i + j < PLANES.  The issuing thread must feed the tensor pipe one MMA every ~64 cycles, so
 // the loops are unrolled at compile time and a descriptor costs one 32-bit add: only the
@@ -188,6 +221,135 @@ __device__ __forceinline__ void issue_slab_any(int planes, uint32_t tmem_d, uint
   if (planes == 3) issue_slab<3>(tmem_d, a_tile, b_tile, idesc, accumulate);
   else if (planes == 2) issue_slab<2>(tmem_d, a_tile, b_tile, idesc, accumulate);
   else issue_slab<1>(tmem_d, a_tile, b_tile, idesc, accumulate);
+}
+
+// Epilogue of one 128 x TN tile by the four epilogue warps: C <- alpha * acc + beta * C with the
+// symmetric-result handling described inside.  `stage_base` is 4 x 32 x STAGE_LD floats of
+// shared memory; the accumulator is waited for on (acc_bar, acc_parity) after the first half of
+// C has been requested.  Returns false when that wait expired.
+template <int TN>
+__device__ __forceinline__ bool epilogue_tile(const float alpha, const float beta, const int64_t ldc, const int M, const int mirror,
+                                              float* __restrict__ C, const int m0, const int n0,
+                                              const int N, const uint32_t tmem_acc, float* stage_base, const int warp,
+                                              const int lane, const bool have_acc, const uint32_t acc_bar,
+                                              const uint32_t acc_parity) {
+  const int q = warp & 3;  // TMEM lane quadrant this warp may read
+  const int row = m0 + q * 32 + lane;
+  const bool vec_ok = (ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+  // whole 32 x TN quadrant in range: coalesced path (uniform in the warp, tcgen05.ld is warp-wide)
+  const bool whole = vec_ok && m0 + q * 32 + 32 <= M && n0 + TN <= N;
+  bool ok = true;
+  bool waited = false;
+  if (whole) {
+    // lane l handles row 4*it + l/8, columns 4*(l%8).. of each 32-column chunk: every global
+    // access of the warp is four full 128-byte row segments.  The first 128 columns of C are
+    // requested before the accumulator is waited for.
+    float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * ldc + n0 + (lane & 7) * 4;
+    // Symmetric result (mirror): the upper triangle is authoritative.  In units of 32 x 32
+    // blocks (gr, gc): gc > gr is stored and also stored transposed, gc == gr is symmetrised
+    // (A_i B_j and A_j B_i are summed in different orders by the MMA), gc < gr is left to the
+    // transposed store of its mirror block.  C[n,m] == C[m,n] then holds bit for bit.
+    const int gr = (m0 >> 5) + q;
+#pragma unroll 1
+    for (int half = 0; half < TN / 128 && ok; ++half) {
+      float4 old[32];
+      if (beta != 0.0f) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int it = 0; it < 8; ++it)
+            old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * ldc + half * 128 + c * 32);
+      }
+      if (!waited) {
+        if (have_acc) ok = mbar_wait(acc_bar, acc_parity, 3);
+        tc_fence_after();
+        waited = true;
+        if (!ok) break;
+      }
+      float* stage = stage_base + (warp - 2) * 32 * STAGE_LD;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        if (have_acc) {
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128 + c * 32), v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        }
+        const int gc = ((n0 + half * 128) >> 5) + c;
+        const bool store_direct = !mirror || gc > gr;
+        const bool store_mirror = mirror && gc > gr;
+        const bool symmetrise = mirror && gc == gr;
+        const int coff = half * 128 + c * 32;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          float* sp = &stage[(4 * it + (lane >> 3)) * STAGE_LD + (lane & 7) * 4];
+          const float4 a4 = *reinterpret_cast<const float4*>(sp);
+          float4 o = make_float4(alpha * a4.x, alpha * a4.y, alpha * a4.z, alpha * a4.w);
+          if (beta != 0.0f) {
+            const float4 od = old[c * 8 + it];
+            o.x = fmaf(beta, od.x, o.x); o.y = fmaf(beta, od.y, o.y);
+            o.z = fmaf(beta, od.z, o.z); o.w = fmaf(beta, od.w, o.w);
+          }
+          if (store_direct) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * ldc + coff) = o;
+          if (mirror) *reinterpret_cast<float4*>(sp) = o;  // keep the final values for the stores below
+        }
+        __syncwarp();
+        if (symmetrise) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = 4 * it + (lane >> 3), cc = (lane & 7) * 4;
+            float e[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) e[t] = (cc + t >= r) ? stage[r * STAGE_LD + cc + t] : stage[(cc + t) * STAGE_LD + r];
+            *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * ldc + coff) = make_float4(e[0], e[1], e[2], e[3]);
+          }
+        }
+        if (store_mirror) {
+          // C[n0 + coff + i][m0 + 32q + l] = final[l][i]: one 128-byte row segment per i
+          float* mq = C + (int64_t)(n0 + coff) * ldc + m0 + q * 32 + lane;
+#pragma unroll 8
+          for (int i = 0; i < 32; ++i) mq[(int64_t)i * ldc] = stage[lane * STAGE_LD + i];
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    if (have_acc) ok = mbar_wait(acc_bar, acc_parity, 3);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        float v[32];
+        if (have_acc) {
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        }
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float* dst = C + (int64_t)row * ldc + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < N) {
+              float o = alpha * v[j];
+              if (beta != 0.0f) o = fmaf(beta, dst[j], o);
+              // symmetric result: the upper triangle is authoritative; inside a diagonal 32 x 32
+              // block the coalesced path symmetrises, so take the element of the upper half there too
+              if (!(mirror && col0 + j < row)) dst[j] = o;
+              if (mirror && col0 + j > row) C[(int64_t)(col0 + j) * ldc + row] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  return ok;
 }
 
 // ---------------------------------------------------------------- the GEMM kernel
@@ -274,131 +436,158 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
       umma_commit(acc_bar);  // arrives when every MMA issued above has completed
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    const bool have_acc = n_slabs > 0;
-    float* __restrict__ C = p.C + (int64_t)b * p.c_bs;
-    const int row = m0 + q * 32 + lane;
-    const bool vec_ok = (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-    // whole 32 x TN quadrant in range: coalesced path (uniform in the warp, tcgen05.ld is warp-wide)
-    const bool whole = vec_ok && m0 + q * 32 + 32 <= p.M && n0 + TN <= N;
-    bool ok = true;
-    bool waited = false;
-    if (whole) {
-      // lane l handles row 4*it + l/8, columns 4*(l%8).. of each 32-column chunk: every global
-      // access of the warp is four full 128-byte row segments.  The first 128 columns of C are
-      // requested before the accumulator is waited for.
-      float* cq = C + (int64_t)(m0 + q * 32 + (lane >> 3)) * p.ldc + n0 + (lane & 7) * 4;
-      // Symmetric result (p.mirror): the upper triangle is authoritative.  In units of 32 x 32
-      // blocks (gr, gc): gc > gr is stored and also stored transposed, gc == gr is symmetrised
-      // (A_i B_j and A_j B_i are summed in different orders by the MMA), gc < gr is left to the
-      // transposed store of its mirror block.  C[n,m] == C[m,n] then holds bit for bit.
-      const int gr = (m0 >> 5) + q;
-#pragma unroll 1
-      for (int half = 0; half < TN / 128 && ok; ++half) {
-        float4 old[32];
-        if (p.beta != 0.0f) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int it = 0; it < 8; ++it)
-              old[c * 8 + it] = *reinterpret_cast<const float4*>(cq + (int64_t)(4 * it) * p.ldc + half * 128 + c * 32);
-        }
-        if (!waited) {
-          if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
-          tc_fence_after();
-          waited = true;
-          if (!ok) break;
-        }
-        // every MMA has completed, so the operand stages are free: stage 0 becomes the staging tiles
-        float* stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (warp - 2) * 32 * STAGE_LD;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          if (have_acc) {
-            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128 + c * 32), v);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-          }
-          const int gc = ((n0 + half * 128) >> 5) + c;
-          const bool store_direct = !p.mirror || gc > gr;
-          const bool store_mirror = p.mirror && gc > gr;
-          const bool symmetrise = p.mirror && gc == gr;
-          const int coff = half * 128 + c * 32;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            float* sp = &stage[(4 * it + (lane >> 3)) * STAGE_LD + (lane & 7) * 4];
-            const float4 a4 = *reinterpret_cast<const float4*>(sp);
-            float4 o = make_float4(p.alpha * a4.x, p.alpha * a4.y, p.alpha * a4.z, p.alpha * a4.w);
-            if (p.beta != 0.0f) {
-              const float4 od = old[c * 8 + it];
-              o.x = fmaf(p.beta, od.x, o.x); o.y = fmaf(p.beta, od.y, o.y);
-              o.z = fmaf(p.beta, od.z, o.z); o.w = fmaf(p.beta, od.w, o.w);
-            }
-            if (store_direct) *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + coff) = o;
-            if (p.mirror) *reinterpret_cast<float4*>(sp) = o;  // keep the final values for the stores below
-          }
-          __syncwarp();
-          if (symmetrise) {
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int r = 4 * it + (lane >> 3), cc = (lane & 7) * 4;
-              float e[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t) e[t] = (cc + t >= r) ? stage[r * STAGE_LD + cc + t] : stage[(cc + t) * STAGE_LD + r];
-              *reinterpret_cast<float4*>(cq + (int64_t)(4 * it) * p.ldc + coff) = make_float4(e[0], e[1], e[2], e[3]);
-            }
-          }
-          if (store_mirror) {
-            // C[n0 + coff + i][m0 + 32q + l] = final[l][i]: one 128-byte row segment per i
-            float* mq = C + (int64_t)(n0 + coff) * p.ldc + m0 + q * 32 + lane;
-#pragma unroll 8
-            for (int i = 0; i < 32; ++i) mq[(int64_t)i * p.ldc] = stage[lane * STAGE_LD + i];
-          }
-          __syncwarp();
-        }
-      }
-    } else {
-      if (have_acc) ok = mbar_wait(acc_bar, 0, 3);
-      tc_fence_after();
-      if (ok) {
-#pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
-          float v[32];
-          if (have_acc) {
-            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-          }
-          const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < N) {
-            float* dst = C + (int64_t)row * p.ldc + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < N) {
-                float o = p.alpha * v[j];
-                if (p.beta != 0.0f) o = fmaf(p.beta, dst[j], o);
-                // symmetric result: the upper triangle is authoritative; inside a diagonal 32 x 32
-                // block the coalesced path symmetrises, so take the element of the upper half there too
-                if (!(p.mirror && col0 + j < row)) dst[j] = o;
-                if (p.mirror && col0 + j > row) C[(int64_t)(col0 + j) * p.ldc + row] = o;
-              }
-            }
-          }
-        }
-      }
-    }
+    // every MMA has completed when the accumulator barrier fires, so the operand stages are
+    // free: stage 0 becomes the staging tiles
+    epilogue_tile<TN>(p.alpha, p.beta, p.ldc, p.M, p.mirror, p.C + (int64_t)b * p.c_bs, m0, n0, N, tmem_acc,
+                      reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))), warp, lane, n_slabs > 0, acc_bar, 0);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_acc, TN);
+  }
+}
+
+// ---------------------------------------------------------------- persistent one-plane GEMM (the Hessian)
+// 128 x 256 tiles, one plane per operand (bf16/fp16 activations), any K.  One CTA per SM walks the
+// list of kept tiles (index = blockIdx.x + i * gridDim.x): the operand ring keeps running across
+// tiles, the accumulator alternates between the two halves of tensor memory, and the epilogue of
+// tile i (read-modify-write of C and, for the symmetric Hessian, the transposed store) runs while
+// tile i+1 is multiplied.  With one tile per CTA the tensor pipe idled through every prologue and
+// epilogue.
+constexpr int PERSIST_TN = 256, PERSIST_STAGES = 4;
+
+// kept tile number w -> tile row ty, tile column tx (row-major over the kept tiles)
+__device__ __forceinline__ void persistent_tile(const UmmaParams& p, int w, int nx_tiles, int& ty, int& tx) {
+  if (!p.upper_tiles_only) {
+    ty = w / nx_tiles;
+    tx = w - ty * nx_tiles;
+    return;
+  }
+  ty = 0;
+  for (;;) {
+    const int tx0 = (ty * TILE_M) / PERSIST_TN;  // first tile of the row that reaches the diagonal
+    const int cnt = nx_tiles - tx0;
+    if (w < cnt) { tx = tx0 + w; return; }
+    w -= cnt;
+    ++ty;
+  }
+}
+
+// DIRECT: the operands are not plane buffers but one row-major 16-bit matrix X (k x m, the
+// activations: tokens x channels) read in place through a 2-D map (map_a; map_b unused) with
+// 64 x 64 boxes, which arrive MN-major; C <- alpha X^T X + beta C.
+template <bool DIRECT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                            const __grid_constant__ CUtensorMap map_b,
+                                                                            const UmmaParams p, const int n_work) {
+  constexpr int TN = PERSIST_TN, NST = PERSIST_STAGES;
+  constexpr uint32_t STAGE = PLANE_TILE_BYTES + TN * SLAB_K * 2;  // A 16 KB + B 32 KB
+  const int nx_tiles = (p.N + TN - 1) / TN;
+  const int n_slabs = (p.K + SLAB_K - 1) / SLAB_K;
+  const int my_tiles = ((int)blockIdx.x < n_work) ? (n_work - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  if (my_tiles == 0) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * NST + 4];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[NST]);
+  const uint32_t acc_full = smem_u32(&bars[2 * NST]), acc_empty = smem_u32(&bars[2 * NST + 2]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full + 8 * s, 1);
+      mbar_init(acc_empty + 8 * s, 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 2 * TN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    int it = 0;
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      int ty, tx;
+      persistent_tile(p, (int)blockIdx.x + i * (int)gridDim.x, nx_tiles, ty, tx);
+      const int a_row = ty * TILE_M + p.a_row0, b_row = tx * TN + p.b_row0;
+      for (int s = 0; s < n_slabs; ++s, ++it) {
+        const int st = it % NST;
+        if (it >= NST && !mbar_wait(empty0 + 8 * st, ((it / NST) - 1) & 1, 31)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(full0 + 8 * st, STAGE);
+          const uint32_t dst = smem_base + (uint32_t)st * STAGE;
+          if (DIRECT) {
+            // boxes of 64 channels x 64 tokens, 8 KB each: two for A, four for B
+#pragma unroll
+            for (int h = 0; h < TILE_M / 64; ++h) tma_load_2d(dst + h * 8192, &map_a, full0 + 8 * st, a_row + h * 64, s * SLAB_K);
+#pragma unroll
+            for (int h = 0; h < TN / 64; ++h)
+              tma_load_2d(dst + PLANE_TILE_BYTES + h * 8192, &map_a, full0 + 8 * st, b_row + h * 64, s * SLAB_K);
+          } else {
+            tma_load_3d(dst, &map_a, full0 + 8 * st, s * SLAB_K + p.a_k0, a_row, 0);
+#pragma unroll
+            for (int h = 0; h < TN / TILE_M; ++h)  // the TMA box is 128 rows
+              tma_load_3d(dst + PLANE_TILE_BYTES + h * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, s * SLAB_K + p.b_k0,
+                          b_row + h * TILE_M, 0);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    int it = 0;
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int acc = i & 1;
+      if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 32);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t accumulate = 0;
+      for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+        const int st = it % NST;
+        ok = mbar_wait(full0 + 8 * st, (it / NST) & 1, 33);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_base = smem_base + (uint32_t)st * STAGE;
+          if (DIRECT) issue_slab_mn(tmem_acc + (uint32_t)(acc * TN), a_base, a_base + PLANE_TILE_BYTES, p.idesc, accumulate);
+          else issue_slab<1>(tmem_acc + (uint32_t)(acc * TN), a_base, a_base + PLANE_TILE_BYTES, p.idesc, accumulate);
+          umma_commit(empty0 + 8 * st);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(acc_full + 8 * acc);
+      __syncwarp();
+    }
+  } else {
+    float* stage_base = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)NST * STAGE);
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int acc = i & 1;
+      int ty, tx;
+      persistent_tile(p, (int)blockIdx.x + i * (int)gridDim.x, nx_tiles, ty, tx);
+      ok = epilogue_tile<TN>(p.alpha, p.beta, p.ldc, p.M, p.mirror, p.C, ty * TILE_M, tx * TN, p.N, tmem_acc + (uint32_t)(acc * TN), stage_base, warp, lane,
+                             n_slabs > 0, acc_full + 8 * acc, (uint32_t)((i >> 1) & 1));
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, 2 * TN);
   }
 }
 
@@ -412,9 +601,6 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
 // so the read-modify-write of C, the B loads and the tensor pipe overlap.
 constexpr int PANEL_MAX_RUN = 16;
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b,
@@ -719,6 +905,36 @@ __global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
   }
 }
 
+// 16-bit activations whose row index is the contiguous one (X stored tokens x channels, wanted as
+// channels x tokens): a plain transposing copy of one plane, 64 x 64 tiles, 128-byte rows on both
+// the global reads and the global writes.  Zero outside (rows, K) up to (rows_pad, K_pad).
+__global__ void __launch_bounds__(256) transpose16_kernel(const uint16_t* __restrict__ src, int64_t cs, int rows, int K,
+                                                          int rows_pad, int K_pad, uint16_t* __restrict__ dst) {
+  __shared__ uint16_t tile[64][66];  // tile[k][r]
+  const int r0 = blockIdx.y * 64, k0 = blockIdx.x * 64;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool pair_ok = (cs & 1) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = k0 + warp + 8 * i, r = r0 + 2 * lane;
+    uint32_t v = 0;
+    if (k < K) {
+      const uint16_t* s = src + (int64_t)k * cs + r;
+      if (pair_ok && r + 1 < rows) v = __ldg(reinterpret_cast<const uint32_t*>(s));
+      else v = (r < rows ? (uint32_t)__ldg(s) : 0u) | (r + 1 < rows ? (uint32_t)__ldg(s + 1) << 16 : 0u);
+    }
+    *reinterpret_cast<uint32_t*>(&tile[warp + 8 * i][2 * lane]) = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + warp + 8 * i, k = k0 + 2 * lane;
+    if (r >= rows_pad || k >= K_pad) continue;  // K_pad is even
+    const uint32_t v = (uint32_t)tile[2 * lane][warp + 8 * i] | ((uint32_t)tile[2 * lane + 1][warp + 8 * i] << 16);
+    *reinterpret_cast<uint32_t*>(dst + (int64_t)r * K_pad + k) = v;
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -797,6 +1013,15 @@ int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t b
   sp.rows = rows; sp.K = K; sp.rows_pad = ps.rows_pad; sp.K_pad = ps.K_pad;
   sp.planes = ps.planes; sp.dst = ps.base; sp.plane_stride = ps.total_rows * ps.K_pad;
   sp.row_total = row_total; sp.row_step = row_step; sp.k_total = k_total; sp.k_step = k_step;
+  if (in_dtype != MQ_F32 && rs == 1 && cs != 1 && batch == 1 && !row_step && !k_step) {
+    // bf16 / fp16 bit patterns pass through unchanged
+    dim3 grid((unsigned)ceil_div(ps.K_pad, 64), (unsigned)ceil_div(ps.rows_pad, 64), 1);
+    ProfScope prof(PROF_SPLIT, (double)ps.rows_pad * ps.K_pad * 4.0, 0.0, st);
+    transpose16_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src), cs, rows, K, ps.rows_pad, ps.K_pad, ps.base);
+    MQ_LAUNCH_CHECK();
+    *out = ps;
+    return MQ_OK;
+  }
   switch (in_dtype) {
     case MQ_F32: MQ_TRY((launch_split<float, __nv_bfloat16>(sp, batch, st))); break;
     case MQ_BF16: MQ_TRY((launch_split<__nv_bfloat16, __nv_bfloat16>(sp, batch, st))); break;
@@ -812,7 +1037,8 @@ int configure_once() {
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_gemm_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
     MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     done[dev & 63] = true;
   }
@@ -887,11 +1113,17 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     MQ_CUDA(launch_chained(true, umma_panel_kernel, pgrid, dim3(GEMM_THREADS), psmem, st, map_a, map_b, map_c, p, run));
   } else {
     if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
-      // one product per element: 128 x 256 tiles, four 48 KB stages
-      p.stages = 4;
-      p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
-      dim3 wgrid((unsigned)ceil_div(d.N, 256), (unsigned)ceil_div(d.M, TILE_M), 1);
-      umma_gemm_kernel<256><<<wgrid, GEMM_THREADS, (size_t)4 * (PLANE_TILE_BYTES + 2 * PLANE_TILE_BYTES) + 1024, st>>>(map_a, map_b, p);
+      // one product per element: 128 x 256 tiles, four 48 KB stages, one persistent CTA per SM
+      p.stages = PERSIST_STAGES;
+      p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(PERSIST_TN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+      const int my_tiles = (int)ceil_div(d.M, TILE_M), nx_tiles = (int)ceil_div(d.N, PERSIST_TN);
+      long long n_work = 0;
+      for (int ty = 0; ty < my_tiles; ++ty) {
+        const int tx0 = d.upper_tiles_only ? (ty * TILE_M) / PERSIST_TN : 0;
+        if (nx_tiles > tx0) n_work += nx_tiles - tx0;
+      }
+      const size_t wsmem = (size_t)PERSIST_STAGES * (PLANE_TILE_BYTES + PERSIST_TN * SLAB_K * 2) + STAGE_BYTES + 1024;
+      umma_gemm_persistent_kernel<false><<<(unsigned)(n_work < 148 ? n_work : 148), GEMM_THREADS, wsmem, st>>>(map_a, map_b, p, (int)n_work);
     } else {
       umma_gemm_kernel<128><<<grid, GEMM_THREADS, smem, st>>>(map_a, map_b, p);
     }
@@ -949,6 +1181,44 @@ size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, i
 int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
                          float alpha, int split, Workspace& ws, cudaStream_t st) {
   MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "mq_hessian_accum: split must be 1, 2 or 3 (got %d)", split);
+  if (x_dtype != MQ_F32 && m > 0 && C >= PERSIST_TN && (ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
+    // 16-bit activations are read where they lie: no transposed copy, no workspace
+    MQ_TRY(configure_once());
+    EncodeTiledFn enc;
+    MQ_TRY(get_encoder(&enc));
+    CUtensorMap map_x;
+    cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_x, x_dtype == MQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                     const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MQ_REQUIRE(r == CUDA_SUCCESS, MQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d for X (tokens=%lld C=%lld ldx=%lld)",
+               (int)r, (long long)m, (long long)C, (long long)ldx);
+    UmmaParams p = {};
+    p.C = H; p.ldc = ldh;
+    p.M = (int)C; p.N = (int)C; p.K = (int)m;
+    p.alpha = alpha; p.beta = beta;
+    p.upper_tiles_only = 1; p.mirror = 1;
+    p.planes = 1; p.nterms = 1; p.stages = PERSIST_STAGES;
+    const uint32_t fmt = x_dtype == MQ_F16 ? 0u : 1u;
+    // both operands MN-major (bits 15 and 16)
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(PERSIST_TN >> 3) << 17) |
+              ((uint32_t)(TILE_M >> 4) << 24);
+    const int my_tiles = (int)ceil_div(C, TILE_M), nx_tiles = (int)ceil_div(C, PERSIST_TN);
+    long long n_work = 0;
+    for (int ty = 0; ty < my_tiles; ++ty) {
+      const int tx0 = (ty * TILE_M) / PERSIST_TN;
+      if (nx_tiles > tx0) n_work += nx_tiles - tx0;
+    }
+    const size_t wsmem = (size_t)PERSIST_STAGES * (PLANE_TILE_BYTES + PERSIST_TN * SLAB_K * 2) + STAGE_BYTES + 1024;
+    ProfScope prof(PROF_UMMA_GEMM, (double)m * C * (C + 1), 2.0 * (double)n_work * TILE_M * PERSIST_TN * pad_to((int)m, SLAB_K), st);
+    umma_gemm_persistent_kernel<true><<<(unsigned)(n_work < 148 ? n_work : 148), GEMM_THREADS, wsmem, st>>>(map_x, map_x, p,
+                                                                                                          (int)n_work);
+    MQ_LAUNCH_CHECK();
+    return MQ_OK;
+  }
   GemmDesc g;
   g.C = H; g.ldc = ldh;
   g.M = (int)C; g.N = (int)C; g.K = (int)m;

@@ -10,7 +10,11 @@
 // bf16 numbers are exact in fp32, so keeping the terms with i + j < planes recovers
 // fp32-grade products (planes = 3: six products, error ~2^-24) on the tensor pipe.
 //
-// Kernel structure (one 128 x 128 output tile per CTA, 192 threads):
+// Three kernels share the pieces below: umma_gemm_kernel (one tile per CTA, any K, planes,
+// batches), umma_gemm_persistent_kernel (one-plane GEMMs and the Hessian: one CTA per SM walks
+// 128 x 256 tiles, epilogue under the next tile's MMAs; 16-bit activations are read in place as
+// MN-major boxes) and umma_panel_kernel (K <= 128, A stationary, C through the TMA unit).
+// Structure of the first (one 128 x 128 output tile per CTA, 192 threads):
 //   warp 0, one lane : TMA producer, fills a ring of shared-memory stages
 //   warp 1, one lane : issues tcgen05.mma (M128 N128 K16) into a 128-column TMEM
 //                      accumulator, releases stages with tcgen05.commit
@@ -353,9 +357,9 @@ __device__ __forceinline__ bool epilogue_tile(const float alpha, const float bet
 }
 
 // ---------------------------------------------------------------- the GEMM kernel
-// TN = 128: any number of planes.  TN = 256: one plane only (bf16/fp16 activations of the
-// Hessian); the wider tile halves the A bytes streamed per flop, which is what limits a
-// one-product GEMM (4 MMAs per 64-wide slab), and leaves room for a 4-stage ring.
+// One 128 x TN tile per CTA, any number of planes, batches, triangular k-ranges.  Instantiated
+// with TN = 128; one-plane GEMMs with N >= 256 go to umma_gemm_persistent_kernel (256-wide tiles
+// halve the A bytes streamed per flop, which is what limits a one-product GEMM).
 template <int TN>
 __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ CUtensorMap map_b,

@@ -49,8 +49,11 @@ __device__ __forceinline__ void split_bf16x3(float x, uint16_t& hi, uint16_t& mi
 int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStream_t st);
 
 // fp32 matrix (rows x K, element (r,k) at src[r*rs + k*cs]) -> planes, zero padded.
+// only_k_blocks_before_rows: write only the part with k in a 128-block in front of the row's own
+// 128-block (the strictly upper blocks of a triangular factor stored transposed); the rest of
+// the buffer stays unwritten and must not be read.
 int make_planes_f32(const float* src, int64_t rs, int64_t cs, int rows, int K, int planes, uint16_t* dst, PlaneSet* out,
-                    cudaStream_t st);
+                    cudaStream_t st, bool only_k_blocks_before_rows = false);
 
 // Tensor-core GEMM on fp32 operands that are split into `split` bf16 planes on the fly.
 int gemm_tensor_f32(const GemmDesc& d, int split, Workspace ws, cudaStream_t st);

@@ -200,7 +200,8 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
     MQ_REQUIRE(ep && up, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small for the operand planes");
     err_set.base = ep; err_set.planes = split; err_set.rows_pad = (int)pad_rows(R); err_set.total_rows = err_set.rows_pad;
     err_set.K_pad = TILE;
-    MQ_TRY(make_planes_f32(Uhat, 1, ldu, (int)C, (int)C, split, up, &u_set, st));
+    // the lazy updates read Uhat[i1:i2, i2:]: only blocks strictly above the diagonal
+    MQ_TRY(make_planes_f32(Uhat, 1, ldu, (int)C, (int)C, split, up, &u_set, st, true));
   }
   uint16_t* const ep_arg = tensor ? err_set.base : nullptr;
   const int64_t ep_stride = tensor ? err_set.total_rows * TILE : 0;

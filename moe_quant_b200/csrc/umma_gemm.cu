@@ -855,6 +855,9 @@ struct SplitParams {
   int64_t plane_stride;
   // ragged last batch (see GemmDesc): rows_b = min(rows, row_total - b*row_step) etc.
   int row_total, row_step, k_total, k_step;
+  // when set, 32 x 32 tiles whose k lies at or beyond the 128-block of their rows are skipped
+  // (left unwritten): the caller only ever reads k-blocks in front of a row's own block
+  int only_k_blocks_before_rows;
 };
 
 template <typename T>
@@ -888,6 +891,7 @@ __global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
   if (p.k_step) { int left = p.k_total - b * p.k_step; K = K < left ? K : left; }
   const TIn* __restrict__ src = static_cast<const TIn*>(p.src) + (int64_t)b * p.bs;
   const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  if (p.only_k_blocks_before_rows && k0 >= (r0 / TILE_M) * TILE_M) return;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   if (TRANSPOSE) {
 #pragma unroll
@@ -1002,7 +1006,8 @@ int launch_split(const SplitParams& sp, int batch, cudaStream_t st) {
 }
 
 int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t bs, int rows, int K, int batch, int planes,
-                int row_total, int row_step, int k_total, int k_step, Workspace& ws, PlaneSet* out, cudaStream_t st) {
+                int row_total, int row_step, int k_total, int k_step, Workspace& ws, PlaneSet* out, cudaStream_t st,
+                bool only_k_blocks_before_rows = false) {
   PlaneSet ps;
   ps.planes = in_dtype == MQ_F32 ? planes : 1;
   ps.rows_pad = pad_to(rows, TILE_M);
@@ -1017,6 +1022,7 @@ int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t b
   sp.rows = rows; sp.K = K; sp.rows_pad = ps.rows_pad; sp.K_pad = ps.K_pad;
   sp.planes = ps.planes; sp.dst = ps.base; sp.plane_stride = ps.total_rows * ps.K_pad;
   sp.row_total = row_total; sp.row_step = row_step; sp.k_total = k_total; sp.k_step = k_step;
+  sp.only_k_blocks_before_rows = only_k_blocks_before_rows ? 1 : 0;
   if (in_dtype != MQ_F32 && rs == 1 && cs != 1 && batch == 1 && !row_step && !k_step) {
     // bf16 / fp16 bit patterns pass through unchanged
     dim3 grid((unsigned)ceil_div(ps.K_pad, 64), (unsigned)ceil_div(ps.rows_pad, 64), 1);
@@ -1146,9 +1152,9 @@ int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, 
 }
 
 int make_planes_f32(const float* src, int64_t rs, int64_t cs, int rows, int K, int planes, uint16_t* dst, PlaneSet* out,
-                    cudaStream_t st) {
+                    cudaStream_t st, bool only_k_blocks_before_rows) {
   Workspace ws(dst, plane_set_bytes(rows, K, planes));
-  return make_planes(src, MQ_F32, rs, cs, 0, rows, K, 1, planes, 0, 0, 0, 0, ws, out, st);
+  return make_planes(src, MQ_F32, rs, cs, 0, rows, K, 1, planes, 0, 0, 0, 0, ws, out, st, only_k_blocks_before_rows);
 }
 
 size_t engine_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split) {

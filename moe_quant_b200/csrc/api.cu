@@ -27,7 +27,7 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
                void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st);
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
-                     Workspace& ws, cudaStream_t st);
+                     Workspace& ws, cudaStream_t st, bool upper_only);
 int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
                          float alpha, int split, Workspace& ws, cudaStream_t st);
 size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, int split);
@@ -105,6 +105,17 @@ static size_t layer_fixed_bytes(int n_tied, int64_t R, int64_t C) {
 }
 }  // namespace mq
 
+namespace mq {
+// dst[r, c] = src[r, c] for c from the start of row r's 128-column block (ld % 4 == 0, 16-byte aligned).
+__global__ void __launch_bounds__(256) copy_upper_blocks_kernel(const float* __restrict__ src, int64_t lds,
+                                                                float* __restrict__ dst, int64_t ldd, int64_t C) {
+  const int64_t r = blockIdx.y;
+  const int64_t c_begin = (r / 128) * 128;
+  for (int64_t c = c_begin + ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; c < C; c += (int64_t)gridDim.x * blockDim.x * 4)
+    *reinterpret_cast<float4*>(dst + r * ldd + c) = __ldg(reinterpret_cast<const float4*>(src + r * lds + c));
+}
+}  // namespace mq
+
 extern "C" size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64_t C, int math, int split_hinv,
                                                     int split_sweep) {
   using namespace mq;
@@ -159,10 +170,13 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   // handle.H, quant.py:314-316).  Only the unit factor Utilde = T diag(T)^-1 of H = T T^T is
   // built: the sweep below runs in its inverse-free form, so the triangular inverse that
   // src/gptq.py:236-242 needs (and mq_hinv_upper provides) is never computed here.
-  MQ_CUDA(cudaMemcpy2DAsync(U, C * sizeof(float), H, ldh * sizeof(float), C * sizeof(float), C, cudaMemcpyDeviceToDevice, st));
+  // The factorisation, the sweep tiles and the lazy updates read nothing below the diagonal
+  // 128-blocks, so that half is neither copied nor zeroed.
+  copy_upper_blocks_kernel<<<dim3(8, (unsigned)C), 256, 0, st>>>(H, ldh, U, C, C);
+  MQ_LAUNCH_CHECK();
   {
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
-    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st));
+    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st, true));
   }
   // sweep                                                       src/gptq_loop.py:141-148
   for (int i = 0; i < n_tied; ++i) {

@@ -355,12 +355,15 @@ __global__ void __launch_bounds__(256) extract_diag_kernel(const float* __restri
 }
 
 // T -> T diag(T)^-1 on the upper triangle (unit diagonal), zeros below it.
+// upper_only: what lies entirely below the diagonal is left as it is instead of being zeroed
+// (the layer path never reads it).
 __global__ void __launch_bounds__(256) scale_columns_kernel(float* __restrict__ H, int64_t C, int64_t ld,
-                                                            const float* __restrict__ diag) {
+                                                            const float* __restrict__ diag, int upper_only) {
   const int64_t r = blockIdx.y;
   if ((C & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) {
     // four columns per thread; what lies entirely below the diagonal is written without being read
     for (int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; c < C; c += (int64_t)gridDim.x * blockDim.x * 4) {
+      if (upper_only && c + 3 < r) continue;
       float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
       if (c + 3 >= r) {
         const float4 v = *reinterpret_cast<const float4*>(H + r * ld + c);
@@ -414,10 +417,10 @@ size_t hinv_workspace_bytes(int64_t C, int math, int split) {
 }
 
 // H (damped, symmetric; upper triangle read) -> unit upper factor Utilde = T diag(T)^-1 in place,
-// zeros below the diagonal.  diag (C floats, device) receives diag(T).  On a non-positive pivot
+// zeros below the diagonal (upper_only: the part below the diagonal blocks is neither read nor written).  diag (C floats, device) receives diag(T).  On a non-positive pivot
 // flags->not_positive is set and the result is replaced by I.
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
-                     Workspace& ws, cudaStream_t st) {
+                     Workspace& ws, cudaStream_t st, bool upper_only) {
   MQ_TRY(configure_once());
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
@@ -466,7 +469,7 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   // ---- T -> unit-diagonal factor
   extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
-  scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag);
+  scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag, upper_only ? 1 : 0);
   MQ_LAUNCH_CHECK();
   identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags);
   MQ_LAUNCH_CHECK();
@@ -478,7 +481,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   float* diag = ws.take<float>(C);
   float* scratch = ws.take<float>((size_t)C * C);
   MQ_REQUIRE(diag && scratch, MQ_ERR_WORKSPACE, "mq_hinv_upper: workspace too small");
-  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st));
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false));
   if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
@@ -546,7 +549,7 @@ extern "C" int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag
   float* diag = ws.take<float>(C);
   MQ_REQUIRE(diag, MQ_ERR_WORKSPACE, "mq_chol_unit_factor: workspace too small");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st));
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false));
   if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return MQ_OK;
 }

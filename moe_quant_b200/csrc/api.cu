@@ -25,9 +25,10 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
-               void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st);
+               void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st,
+               const float* col_div);
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
-                     Workspace& ws, cudaStream_t st, bool upper_only);
+                     Workspace& ws, cudaStream_t st, bool upper_only, bool unscaled);
 int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
                          float alpha, int split, Workspace& ws, cudaStream_t st);
 size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, int split);
@@ -170,20 +171,23 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   // handle.H, quant.py:314-316).  Only the unit factor Utilde = T diag(T)^-1 of H = T T^T is
   // built: the sweep below runs in its inverse-free form, so the triangular inverse that
   // src/gptq.py:236-242 needs (and mq_hinv_upper provides) is never computed here.
+  // With tensor math the factor's columns are not scaled in a pass of their own: the sweep divides
+  // by diag(T) where it reads the factor (plane split, tile staging), with the same division.
+  const bool unscaled = math == MQ_MATH_TENSOR;
   // The factorisation, the sweep tiles and the lazy updates read nothing below the diagonal
   // 128-blocks, so that half is neither copied nor zeroed.
   copy_upper_blocks_kernel<<<dim3(8, (unsigned)C), 256, 0, st>>>(H, ldh, U, C, C);
   MQ_LAUNCH_CHECK();
   {
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
-    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st, true));
+    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st, true, unscaled));
   }
   // sweep                                                       src/gptq_loop.py:141-148
   for (int i = 0; i < n_tied; ++i) {
     MQ_CUDA(cudaMemcpyAsync(Wo[i], Wf[i], (size_t)R * C * sizeof(float), cudaMemcpyDeviceToDevice, st));
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
     MQ_TRY(gptq_sweep(Wf[i], R, C, C, U, C, scale_out[i], nullptr, group, C / group, 1, bits, w_dtype, codes[i],
-                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st));
+                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st, unscaled ? diag : nullptr));
   }
   return MQ_OK;
 }

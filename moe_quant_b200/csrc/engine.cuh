@@ -51,9 +51,10 @@ int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, 
 // fp32 matrix (rows x K, element (r,k) at src[r*rs + k*cs]) -> planes, zero padded.
 // only_k_blocks_before_rows: write only the part with k in a 128-block in front of the row's own
 // 128-block (the strictly upper blocks of a triangular factor stored transposed); the rest of
-// the buffer stays unwritten and must not be read.
+// the buffer stays unwritten and must not be read.  row_div (optional, device): destination row r is
+// divided by row_div[r] before the split.
 int make_planes_f32(const float* src, int64_t rs, int64_t cs, int rows, int K, int planes, uint16_t* dst, PlaneSet* out,
-                    cudaStream_t st, bool only_k_blocks_before_rows = false);
+                    cudaStream_t st, bool only_k_blocks_before_rows = false, const float* row_div = nullptr);
 
 // Tensor-core GEMM on fp32 operands that are split into `split` bf16 planes on the fly.
 int gemm_tensor_f32(const GemmDesc& d, int split, Workspace ws, cudaStream_t st);

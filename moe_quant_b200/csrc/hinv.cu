@@ -384,8 +384,11 @@ __global__ void __launch_bounds__(256) scale_columns_kernel(float* __restrict__ 
 }
 
 __global__ void __launch_bounds__(256) identity_if_failed_kernel(float* __restrict__ U, int64_t C, int64_t ld,
-                                                                 const mq_layer_flags* flags) {
+                                                                 const mq_layer_flags* flags, float* __restrict__ diag) {
   if (flags->not_positive == 0) return;
+  // with the identity as factor its column scaling is 1 as well (a caller that was handed the
+  // unscaled factor divides by it)
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < C; i += (int64_t)gridDim.x * blockDim.x) diag[i] = 1.0f;
   int64_t n = C * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i / C, c = i - r * C;
@@ -417,10 +420,11 @@ size_t hinv_workspace_bytes(int64_t C, int math, int split) {
 }
 
 // H (damped, symmetric; upper triangle read) -> unit upper factor Utilde = T diag(T)^-1 in place,
-// zeros below the diagonal (upper_only: the part below the diagonal blocks is neither read nor written).  diag (C floats, device) receives diag(T).  On a non-positive pivot
+// zeros below the diagonal (upper_only: the part below the diagonal blocks is neither read nor written;
+// unscaled: T itself is left in place and the caller divides column c by diag[c] where it reads it).  diag (C floats, device) receives diag(T).  On a non-positive pivot
 // flags->not_positive is set and the result is replaced by I.
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
-                     Workspace& ws, cudaStream_t st, bool upper_only) {
+                     Workspace& ws, cudaStream_t st, bool upper_only, bool unscaled) {
   MQ_TRY(configure_once());
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
@@ -469,9 +473,11 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   // ---- T -> unit-diagonal factor
   extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
-  scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag, upper_only ? 1 : 0);
-  MQ_LAUNCH_CHECK();
-  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags);
+  if (!unscaled) {
+    scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag, upper_only ? 1 : 0);
+    MQ_LAUNCH_CHECK();
+  }
+  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags, diag);
   MQ_LAUNCH_CHECK();
   return MQ_OK;
 }
@@ -481,7 +487,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   float* diag = ws.take<float>(C);
   float* scratch = ws.take<float>((size_t)C * C);
   MQ_REQUIRE(diag && scratch, MQ_ERR_WORKSPACE, "mq_hinv_upper: workspace too small");
-  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false));
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false, false));
   if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
@@ -511,7 +517,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
     g2.batch = batch; g2.n_total = (int)(C - s); g2.n_step = (int)(2 * s);
     MQ_TRY(eng.gemm(g2));
   }
-  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(Uhat, C, ldu, flags);
+  identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(Uhat, C, ldu, flags, diag);
   MQ_LAUNCH_CHECK();
   return MQ_OK;
 }
@@ -549,7 +555,7 @@ extern "C" int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag
   float* diag = ws.take<float>(C);
   MQ_REQUIRE(diag, MQ_ERR_WORKSPACE, "mq_chol_unit_factor: workspace too small");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false));
+  MQ_TRY(chol_unit_factor(H, C, ldh, diag, math, split, flags, ws, st, false, false));
   if (diag_out) MQ_CUDA(cudaMemcpyAsync(diag_out, diag, C * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return MQ_OK;
 }

@@ -858,6 +858,8 @@ struct SplitParams {
   // when set, 32 x 32 tiles whose k lies at or beyond the 128-block of their rows are skipped
   // (left unwritten): the caller only ever reads k-blocks in front of a row's own block
   int only_k_blocks_before_rows;
+  // optional: every element of destination row r is divided by row_div[r] before it is split
+  const float* row_div;
 };
 
 template <typename T>
@@ -897,7 +899,9 @@ __global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       int r = r0 + tx, k = k0 + ty + 8 * i;
-      tile[ty + 8 * i][tx] = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+      float x = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+      if (p.row_div && r < rows) x = x / p.row_div[r];
+      tile[ty + 8 * i][tx] = x;
     }
     __syncthreads();
   }
@@ -908,7 +912,10 @@ __global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
     if (r >= p.rows_pad || k >= p.K_pad) continue;
     float x;
     if (TRANSPOSE) x = tile[tx][rl];
-    else x = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+    else {
+      x = (r < rows && k < K) ? to_float(src[(int64_t)r * p.rs + (int64_t)k * p.cs]) : 0.0f;
+      if (p.row_div && r < rows) x = x / p.row_div[r];
+    }
     split_store<TPlane>(x, p.planes, p.dst, ((int64_t)b * p.rows_pad + r) * p.K_pad + k, p.plane_stride);
   }
 }
@@ -1007,7 +1014,7 @@ int launch_split(const SplitParams& sp, int batch, cudaStream_t st) {
 
 int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t bs, int rows, int K, int batch, int planes,
                 int row_total, int row_step, int k_total, int k_step, Workspace& ws, PlaneSet* out, cudaStream_t st,
-                bool only_k_blocks_before_rows = false) {
+                bool only_k_blocks_before_rows = false, const float* row_div = nullptr) {
   PlaneSet ps;
   ps.planes = in_dtype == MQ_F32 ? planes : 1;
   ps.rows_pad = pad_to(rows, TILE_M);
@@ -1023,6 +1030,7 @@ int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t b
   sp.planes = ps.planes; sp.dst = ps.base; sp.plane_stride = ps.total_rows * ps.K_pad;
   sp.row_total = row_total; sp.row_step = row_step; sp.k_total = k_total; sp.k_step = k_step;
   sp.only_k_blocks_before_rows = only_k_blocks_before_rows ? 1 : 0;
+  sp.row_div = row_div;
   if (in_dtype != MQ_F32 && rs == 1 && cs != 1 && batch == 1 && !row_step && !k_step) {
     // bf16 / fp16 bit patterns pass through unchanged
     dim3 grid((unsigned)ceil_div(ps.K_pad, 64), (unsigned)ceil_div(ps.rows_pad, 64), 1);
@@ -1152,9 +1160,9 @@ int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, 
 }
 
 int make_planes_f32(const float* src, int64_t rs, int64_t cs, int rows, int K, int planes, uint16_t* dst, PlaneSet* out,
-                    cudaStream_t st, bool only_k_blocks_before_rows) {
+                    cudaStream_t st, bool only_k_blocks_before_rows, const float* row_div) {
   Workspace ws(dst, plane_set_bytes(rows, K, planes));
-  return make_planes(src, MQ_F32, rs, cs, 0, rows, K, 1, planes, 0, 0, 0, 0, ws, out, st, only_k_blocks_before_rows);
+  return make_planes(src, MQ_F32, rs, cs, 0, rows, K, 1, planes, 0, 0, 0, 0, ws, out, st, only_k_blocks_before_rows, row_div);
 }
 
 size_t engine_workspace_bytes(int64_t M, int64_t N, int64_t K, int math, int split) {

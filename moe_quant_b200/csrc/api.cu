@@ -171,8 +171,8 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   // handle.H, quant.py:314-316).  Only the unit factor Utilde = T diag(T)^-1 of H = T T^T is
   // built: the sweep below runs in its inverse-free form, so the triangular inverse that
   // src/gptq.py:236-242 needs (and mq_hinv_upper provides) is never computed here.
-  // With tensor math the factor's columns are not scaled in a pass of their own: the sweep divides
-  // by diag(T) where it reads the factor (plane split, tile staging), with the same division.
+  // With tensor math only the diagonal blocks of the factor are scaled by 1/diag(T) (the sweep
+  // tiles read them); the blocks above are divided where they are split into planes.
   const bool unscaled = math == MQ_MATH_TENSOR;
   // The factorisation, the sweep tiles and the lazy updates read nothing below the diagonal
   // 128-blocks, so that half is neither copied nor zeroed.

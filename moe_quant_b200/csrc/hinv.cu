@@ -355,29 +355,41 @@ __global__ void __launch_bounds__(256) extract_diag_kernel(const float* __restri
 }
 
 // T -> T diag(T)^-1 on the upper triangle (unit diagonal), zeros below it.
-// upper_only: what lies entirely below the diagonal is left as it is instead of being zeroed
-// (the layer path never reads it).
+// upper_only = 1: what lies entirely below the diagonal is left as it is instead of being zeroed
+// (the layer path never reads it); = 2: in addition only the diagonal 128-blocks are scaled (the
+// sweep tiles read those; the blocks above are divided by whoever splits them into planes).
+__device__ __forceinline__ void scale_quad(float* __restrict__ H, int64_t ld, const float* __restrict__ diag, int64_t r,
+                                           int64_t c) {
+  // four columns c..c+3 of row r; what lies entirely below the diagonal is written without being read
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c + 3 >= r) {
+    const float4 v = *reinterpret_cast<const float4*>(H + r * ld + c);
+    const float4 d = __ldg(reinterpret_cast<const float4*>(diag + c));
+    o.x = (c + 0 > r) ? v.x / d.x : (c + 0 == r ? 1.0f : 0.0f);
+    o.y = (c + 1 > r) ? v.y / d.y : (c + 1 == r ? 1.0f : 0.0f);
+    o.z = (c + 2 > r) ? v.z / d.z : (c + 2 == r ? 1.0f : 0.0f);
+    o.w = (c + 3 > r) ? v.w / d.w : (c + 3 == r ? 1.0f : 0.0f);
+  }
+  *reinterpret_cast<float4*>(H + r * ld + c) = o;
+}
+
 __global__ void __launch_bounds__(256) scale_columns_kernel(float* __restrict__ H, int64_t C, int64_t ld,
                                                             const float* __restrict__ diag, int upper_only) {
   const int64_t r = blockIdx.y;
   if ((C & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) {
-    // four columns per thread; what lies entirely below the diagonal is written without being read
+    if (upper_only == 2) {  // launched with one block of 32 threads per row: the row's diagonal block
+      const int64_t c = (r / NB) * NB + threadIdx.x * 4;
+      if (blockIdx.x == 0 && threadIdx.x < NB / 4 && c < C && c + 3 >= r) scale_quad(H, ld, diag, r, c);
+      return;
+    }
     for (int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; c < C; c += (int64_t)gridDim.x * blockDim.x * 4) {
       if (upper_only && c + 3 < r) continue;
-      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c + 3 >= r) {
-        const float4 v = *reinterpret_cast<const float4*>(H + r * ld + c);
-        const float4 d = __ldg(reinterpret_cast<const float4*>(diag + c));
-        o.x = (c + 0 > r) ? v.x / d.x : (c + 0 == r ? 1.0f : 0.0f);
-        o.y = (c + 1 > r) ? v.y / d.y : (c + 1 == r ? 1.0f : 0.0f);
-        o.z = (c + 2 > r) ? v.z / d.z : (c + 2 == r ? 1.0f : 0.0f);
-        o.w = (c + 3 > r) ? v.w / d.w : (c + 3 == r ? 1.0f : 0.0f);
-      }
-      *reinterpret_cast<float4*>(H + r * ld + c) = o;
+      scale_quad(H, ld, diag, r, c);
     }
     return;
   }
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < C; c += (int64_t)gridDim.x * blockDim.x) {
+    if (upper_only == 2 && (c < (r / NB) * NB || c >= (r / NB + 1) * NB)) continue;
     float v = H[r * ld + c];
     H[r * ld + c] = (c > r) ? v / diag[c] : (c == r ? 1.0f : 0.0f);
   }
@@ -421,7 +433,8 @@ size_t hinv_workspace_bytes(int64_t C, int math, int split) {
 
 // H (damped, symmetric; upper triangle read) -> unit upper factor Utilde = T diag(T)^-1 in place,
 // zeros below the diagonal (upper_only: the part below the diagonal blocks is neither read nor written;
-// unscaled: T itself is left in place and the caller divides column c by diag[c] where it reads it).  diag (C floats, device) receives diag(T).  On a non-positive pivot
+// unscaled: only the diagonal blocks are scaled; above them T itself is left in place and the caller
+// divides column c by diag[c] where it reads it).  diag (C floats, device) receives diag(T).  On a non-positive pivot
 // flags->not_positive is set and the result is replaced by I.
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
                      Workspace& ws, cudaStream_t st, bool upper_only, bool unscaled) {
@@ -473,8 +486,10 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   // ---- T -> unit-diagonal factor
   extract_diag_kernel<<<(unsigned)ceil_div(C, 256), 256, 0, st>>>(H, C, ldh, diag);
   MQ_LAUNCH_CHECK();
-  if (!unscaled) {
-    scale_columns_kernel<<<dim3((unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8), (unsigned)C), 256, 0, st>>>(H, C, ldh, diag, upper_only ? 1 : 0);
+  {
+    const int mode = unscaled ? 2 : (upper_only ? 1 : 0);
+    const unsigned gx = unscaled ? 1u : (unsigned)(ceil_div(C, 256) < 8 ? ceil_div(C, 256) : 8);
+    scale_columns_kernel<<<dim3(gx, (unsigned)C), unscaled ? 32 : 256, 0, st>>>(H, C, ldh, diag, mode);
     MQ_LAUNCH_CHECK();
   }
   identity_if_failed_kernel<<<148 * 4, 256, 0, st>>>(H, C, ldh, flags, diag);

@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     float maxq, float zero_default, uint8_t* __restrict__ codes, int64_t C,
     typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb,
     const float* __restrict__ Worig, int64_t ldwo, uint16_t* __restrict__ err_planes, int64_t plane_stride,
-    int n_planes, const float* __restrict__ col_div) {
+    int n_planes) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
   // The factor is constant during the sweep: its tile is staged before this grid waits for the
@@ -41,10 +41,6 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (j < nb && k4 < nb && k4 + 3 > j) {
       v = __ldg(reinterpret_cast<const float4*>(U + (int64_t)(i1 + j) * ldu + i1 + k4));
-      if (col_div) {  // the factor was left unscaled: column c is divided by col_div[c] here
-        const float4 d = __ldg(reinterpret_cast<const float4*>(col_div + i1 + k4));
-        v.x = v.x / d.x; v.y = v.y / d.y; v.z = v.z / d.z; v.w = v.w / d.w;
-      }
       if (k4 + 0 <= j) v.x = 0.f;
       if (k4 + 1 <= j) v.y = 0.f;
       if (k4 + 2 <= j) v.z = 0.f;
@@ -189,8 +185,9 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
                void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st,
                const float* col_div) {
-  // col_div (tensor math only): Uhat holds the factor before its columns were divided by col_div;
-  // the plane split and the tile staging divide where they read it.
+  // col_div (tensor math only): above its diagonal 128-blocks Uhat holds the factor before its
+  // columns were divided by col_div; the plane split divides where it reads it.  The diagonal
+  // blocks, which the tiles read, are already scaled.
   MQ_TRY(configure_once());
   float* err = ws.take<float>((size_t)R * TILE);
   MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
@@ -228,17 +225,17 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       case MQ_F32:
         MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F32>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<float*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split, col_div));
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       case MQ_BF16:
         MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_BF16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                    maxq, zero_default, codes, C,
-                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split, col_div));
+                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
         break;
       default:
         MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
                                                                   maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split, col_div));
+                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
     }
     }
     MQ_LAUNCH_CHECK();

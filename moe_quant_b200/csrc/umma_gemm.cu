@@ -920,6 +920,46 @@ __global__ void __launch_bounds__(256) split_planes_kernel(SplitParams p) {
   }
 }
 
+// fp32 source whose row index is the contiguous one (a row-major matrix wanted transposed, the
+// triangular factor for the sweep) -> up to three bf16 planes.  64 x 64 tiles: 256-byte rows on
+// the global reads, 128-byte rows per plane on the writes, two k per thread.
+__global__ void __launch_bounds__(256) split_transposed_f32_kernel(SplitParams p) {
+  __shared__ float tile[64][65];  // tile[k][r]
+  const int r0 = blockIdx.y * 64, k0 = blockIdx.x * 64;
+  if (p.only_k_blocks_before_rows && k0 >= (r0 / TILE_M) * TILE_M) return;
+  const float* __restrict__ src = static_cast<const float*>(p.src);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = k0 + warp + 8 * i;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + lane + 32 * h;
+      tile[warp + 8 * i][lane + 32 * h] = (r < p.rows && k < p.K) ? __ldg(src + (int64_t)r * p.rs + (int64_t)k * p.cs) : 0.0f;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = warp + 8 * i;
+    const int r = r0 + rl, k = k0 + 2 * lane;
+    if (r >= p.rows_pad || k >= p.K_pad) continue;  // K_pad is even
+    float x0 = tile[2 * lane][rl], x1 = tile[2 * lane + 1][rl];
+    if (p.row_div && r < p.rows) {
+      const float d = __ldg(p.row_div + r);
+      x0 = x0 / d;
+      x1 = x1 / d;
+    }
+    uint16_t h0, m0, l0, h1, m1, l1;
+    split_bf16x3(x0, h0, m0, l0);
+    split_bf16x3(x1, h1, m1, l1);
+    uint16_t* dst = p.dst + (int64_t)r * p.K_pad + k;
+    *reinterpret_cast<uint32_t*>(dst) = (uint32_t)h0 | ((uint32_t)h1 << 16);
+    if (p.planes > 1) *reinterpret_cast<uint32_t*>(dst + p.plane_stride) = (uint32_t)m0 | ((uint32_t)m1 << 16);
+    if (p.planes > 2) *reinterpret_cast<uint32_t*>(dst + 2 * p.plane_stride) = (uint32_t)l0 | ((uint32_t)l1 << 16);
+  }
+}
+
 // 16-bit activations whose row index is the contiguous one (X stored tokens x channels, wanted as
 // channels x tokens): a plain transposing copy of one plane, 64 x 64 tiles, 128-byte rows on both
 // the global reads and the global writes.  Zero outside (rows, K) up to (rows_pad, K_pad).
@@ -1036,6 +1076,14 @@ int make_planes(const void* src, int in_dtype, int64_t rs, int64_t cs, int64_t b
     dim3 grid((unsigned)ceil_div(ps.K_pad, 64), (unsigned)ceil_div(ps.rows_pad, 64), 1);
     ProfScope prof(PROF_SPLIT, (double)ps.rows_pad * ps.K_pad * 4.0, 0.0, st);
     transpose16_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src), cs, rows, K, ps.rows_pad, ps.K_pad, ps.base);
+    MQ_LAUNCH_CHECK();
+    *out = ps;
+    return MQ_OK;
+  }
+  if (in_dtype == MQ_F32 && rs == 1 && cs != 1 && batch == 1 && !row_step && !k_step) {
+    dim3 grid((unsigned)ceil_div(ps.K_pad, 64), (unsigned)ceil_div(ps.rows_pad, 64), 1);
+    ProfScope prof(PROF_SPLIT, (double)ps.rows_pad * ps.K_pad * (4.0 + 2.0 * ps.planes), 0.0, st);
+    split_transposed_f32_kernel<<<grid, 256, 0, st>>>(sp);
     MQ_LAUNCH_CHECK();
     *out = ps;
     return MQ_OK;

@@ -49,7 +49,7 @@ def quantize_block(
     tie_gptq_handles: bool = False,
     save_dir: Optional[str] = None,
     log_error: bool = False,
-    streams: int = 4,
+    streams: int = 8,
     forward_kwargs: Optional[dict] = None,
 ) -> Dict[str, object]:
     """Returns {'outputs': block outputs after quantization (the next block's inputs),

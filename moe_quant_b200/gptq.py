@@ -303,7 +303,7 @@ def _side_streams(device: torch.device, n: int):
 
 
 @torch.no_grad()
-def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 4) -> List[Tuple[Tensor, Tensor, Tensor]]:
+def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 8) -> List[Tuple[Tensor, Tensor, Tensor]]:
     """Quantizes independent, non-distributed handles (the routed experts of a rank,
     quant.py:351-387) round-robin on `streams` CUDA streams.  One layer's GPTQ is a long chain of
     dependent kernels, many of them too small to fill 148 SMs; chains of different layers have no

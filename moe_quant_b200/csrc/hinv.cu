@@ -151,10 +151,17 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
         const float4 j1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8 + 4]);
         const float pi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
         const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
+        // two columns per instruction (packed fp32 FMA: each half is an ordinary fma.rn)
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 8; ++i) {
+          const float2 npi = make_float2(-pi[i], -pi[i]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-pi[i], pj[j], a[i][j]);
+          for (int j = 0; j < 8; j += 2) {
+            const float2 r2 = __ffma2_rn(npi, make_float2(pj[j], pj[j + 1]), make_float2(a[i][j], a[i][j + 1]));
+            a[i][j] = r2.x;
+            a[i][j + 1] = r2.y;
+          }
+        }
       }
     }
   }
@@ -290,10 +297,11 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
 #pragma unroll
         for (int h = 0; h < ROWS; ++h) {
           const float ak = __shfl_sync(0xffffffffu, a[h][kk], kq);
-          a[h][0] = fmaf(-ak, tt.x, a[h][0]);
-          a[h][1] = fmaf(-ak, tt.y, a[h][1]);
-          a[h][2] = fmaf(-ak, tt.z, a[h][2]);
-          a[h][3] = fmaf(-ak, tt.w, a[h][3]);
+          // packed fp32 FMA: two columns per instruction, each half an ordinary fma.rn
+          const float2 nak = make_float2(-ak, -ak);
+          const float2 lo = __ffma2_rn(nak, make_float2(tt.x, tt.y), make_float2(a[h][0], a[h][1]));
+          const float2 hi = __ffma2_rn(nak, make_float2(tt.z, tt.w), make_float2(a[h][2], a[h][3]));
+          a[h][0] = lo.x; a[h][1] = lo.y; a[h][2] = hi.x; a[h][3] = hi.y;
         }
       }
     }

@@ -98,7 +98,7 @@ class ClockSampler:
             self._stop.wait(self.period)
 
     def __enter__(self):
-        self.samples, self.recording = [], True
+        self.recording = True          # samples add up over several timed stretches
         return self
 
     def __exit__(self, *exc):
@@ -229,29 +229,42 @@ def run_b200(args):
     # every block the timed pass will ask for.  A cudaMalloc inside the timed region goes
     # through the driver's global lock, which other jobs on a shared host can hold for tens of
     # milliseconds at a time.
-    warmup = max(warmup, steps)
-    pre = make_handles(warmup)
+    # Every step needs its own copy of a Hessian (quantize damps it in place) and keeps its
+    # results: about 225 MB per step.  A step count that would not fit in memory is timed in
+    # chunks (each bracketed by barrier + synchronize, their device times added up); the default
+    # and anything up to a few hundred steps is one chunk.
+    free_bytes, _total = torch.cuda.mem_get_info(dev)
+    chunk = max(n_streams, min(steps, int(0.6 * free_bytes / 225e6)))
+    warmup = max(warmup, min(steps, chunk))
+    pre = make_handles(min(warmup, chunk))
     pre_results = quantize_many(pre, BITS, streams=n_streams)
     barrier()
     del pre, pre_results
-    handles = make_handles(steps)
-    barrier()
     launches0 = _lib.lib().mq_launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with clocks:
-        ev0.record()
-        results = quantize_many(handles, BITS, streams=n_streams)
-        ev1.record()
+    ms_total, done, issues = 0.0, 0, 0
+    while done < steps:
+        n = min(chunk, steps - done)
+        handles = make_handles(n)
         barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with clocks:
+            ev0.record()
+            results = quantize_many(handles, BITS, streams=n_streams)
+            ev1.record()
+            barrier()
+        ms_total += ev0.elapsed_time(ev1)
+        issues += sum(h.has_hessian_issues() for h in handles)
+        done += n
+        del handles, results
     clocks.close()
-    ms_total = ev0.elapsed_time(ev1)
     launches = _lib.lib().mq_launch_count() - launches0
+    steps_aux = min(steps, 48)             # the secondary rates below are measured on at most 48 steps
     # the same K calls one after the other on one stream (what a plain `for handle: quantize` loop gets)
-    seq_pre = make_handles(steps)          # same untimed pass first, for the same reason
+    seq_pre = make_handles(steps_aux)      # same untimed pass first, for the same reason
     seq_pre_results = [h.quantize(BITS) for h in seq_pre]
     barrier()
     del seq_pre, seq_pre_results
-    seq_handles = make_handles(steps)
+    seq_handles = make_handles(steps_aux)
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s0.record()
@@ -260,14 +273,12 @@ def run_b200(args):
     barrier()
     ms_single = s0.elapsed_time(s1)
     del seq_handles, seq_results
-    issues = sum(h.has_hessian_issues() for h in handles)
     fault = _lib.engine_fault()
-    del handles, results
 
     # ---- gate_proj + up_proj of an expert share their input, hence their Hessian: quantized as a
     # tied pair they share one factorisation (quant.py --tie_gptq_handles; the reference factors twice)
     from moe_quant_b200 import quantize_tied
-    n_pairs = max(2, steps // 4)
+    n_pairs = max(2, steps_aux // 4)
     pair_pool = [torch.cuda.Stream(device=dev) for _ in range(min(n_streams, n_pairs))]
 
     def make_pairs(n):
@@ -400,7 +411,7 @@ def run_b200(args):
         for st in pool:
             cur.wait_stream(st)
 
-    e2e_steps = steps
+    e2e_steps = steps_aux
     e2e_run(max(e2e_steps, n_streams))
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -428,7 +439,7 @@ def run_b200(args):
             "config": {"workload": WORKLOAD, "experts_rotated": n_experts, "tokens_per_expert": tokens,
                        "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
                        "parallelism": f"ep{world}", "streams": n_streams,
-                       "single_stream_layers_per_s_per_gpu": steps / (ms_single / 1e3),
+                       "single_stream_layers_per_s_per_gpu": steps_aux / (ms_single / 1e3),
                        "tied_gate_up_layers_per_s_per_gpu": tied_layers_per_s, "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
             "roofline": roofline, "kernel_time_shares": shares,
             "cpu_baseline": cpu,

@@ -275,6 +275,53 @@ def run_b200(args):
     del seq_handles, seq_results
     fault = _lib.engine_fault()
 
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * steps / (ms_max / 1e3)
+
+    # ---- per-kernel pass (same work, events around every launch of the hot kernels), on one stream
+    # directly after the one-stream pass: the library then sizes its grids as for a single caller
+    prof_handles = make_handles(min(steps, 4))
+    torch.cuda.synchronize()
+    _lib.profile_begin()
+    for h in prof_handles:
+        h.quantize(BITS)
+    prof = _lib.profile_end()
+    del prof_handles
+    peaks = _peaks()
+    kinds = {k: v for k, v in prof.items() if v["launches"]}
+    top = max(kinds, key=lambda k: kinds[k]["ms"]) if kinds else None
+    roofline, shares = None, {}
+    if top:
+        tot = sum(v["ms"] for v in kinds.values())
+        shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
+        v = kinds[top]
+        if top in ("umma_gemm", "simt_gemm"):
+            secs = v["ms"] / 1e3
+            products = 6.0 if top == "umma_gemm" else 1.0     # bf16 products per fp32 product with three planes
+            achieved = v["work"] * products / secs / 1e12
+            # DRAM bytes per 128x128 output tile of a rank-128 update from the committed ncu capture
+            # (141.1 MB for 1485 tiles, profiles/umma_panel_kernel_trailing_update_7168.md); traffic
+            # grows with the tile count, so the average launch is scaled by its tiles
+            tiles_per_launch = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
+            roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
+                        "traffic": 95.0e3 * tiles_per_launch if top == "umma_gemm" else None,
+                        "traffic_note": "bytes per average launch, scaled by tiles from an ncu capture of two large launches",
+                        "fp32_equivalent_tflops": v["work"] / secs / 1e12,
+                        "padded_tflops": v["work2"] / secs / 1e12,
+                        "note": "algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products "
+                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once",
+                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
+                        "peak_source": peaks["source"] + " (sustained bf16)"}
+        else:
+            achieved = v["work"] / (v["ms"] / 1e3) / 1e9
+            roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm"], "traffic": None, "avg_launch_us": v["ms"] / v["launches"] * 1e3,
+                        "peak_source": peaks["source"]}
+
     # ---- gate_proj + up_proj of an expert share their input, hence their Hessian: quantized as a
     # tied pair they share one factorisation (quant.py --tie_gptq_handles; the reference factors twice)
     from moe_quant_b200 import quantize_tied
@@ -316,52 +363,6 @@ def run_b200(args):
     barrier()
     tied_layers_per_s = 2 * n_pairs / (p0.elapsed_time(p1) / 1e3)
     del pairs, pair_results
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    value = world * steps / (ms_max / 1e3)
-
-    # ---- per-kernel pass (same work, events around every launch of the hot kernels)
-    prof_handles = make_handles(min(steps, 4))
-    torch.cuda.synchronize()
-    _lib.profile_begin()
-    for h in prof_handles:
-        h.quantize(BITS)
-    prof = _lib.profile_end()
-    del prof_handles
-    peaks = _peaks()
-    kinds = {k: v for k, v in prof.items() if v["launches"]}
-    top = max(kinds, key=lambda k: kinds[k]["ms"]) if kinds else None
-    roofline, shares = None, {}
-    if top:
-        tot = sum(v["ms"] for v in kinds.values())
-        shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
-        v = kinds[top]
-        if top in ("umma_gemm", "simt_gemm"):
-            secs = v["ms"] / 1e3
-            products = 6.0 if top == "umma_gemm" else 1.0     # bf16 products per fp32 product with three planes
-            achieved = v["work"] * products / secs / 1e12
-            # DRAM bytes per 128x128 output tile of a rank-128 update from the committed ncu capture
-            # (141.1 MB for 1485 tiles, profiles/umma_panel_kernel_trailing_update_7168.md); traffic
-            # grows with the tile count, so the average launch is scaled by its tiles
-            tiles_per_launch = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
-            roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
-                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
-                        "traffic": 95.0e3 * tiles_per_launch if top == "umma_gemm" else None,
-                        "traffic_note": "bytes per average launch, scaled by tiles from an ncu capture of two large launches",
-                        "fp32_equivalent_tflops": v["work"] / secs / 1e12,
-                        "padded_tflops": v["work2"] / secs / 1e12,
-                        "note": "algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products "
-                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once",
-                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
-                        "peak_source": peaks["source"] + " (sustained bf16)"}
-        else:
-            achieved = v["work"] / (v["ms"] / 1e3) / 1e9
-            roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                        "frac": achieved / peaks["hbm"], "traffic": None, "avg_launch_us": v["ms"] / v["launches"] * 1e3,
-                        "peak_source": peaks["source"]}
-
     # ---- Hessian accumulation rate (the second half of the headline metric)
     g = torch.Generator(device=dev).manual_seed(seed)
     X = (torch.randn(TOKENS, C, generator=g, device=dev)).to(torch.bfloat16)

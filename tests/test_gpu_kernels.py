@@ -113,6 +113,29 @@ def test_hessian_accum_ragged(cuda, precision, m, C, dtype):
     assert float(err) < 5e-6   # tensor-core fp32 accumulation truncates; fp32 FMA path reaches ~3e-7
 
 
+@pytest.mark.parametrize("pad,offset", [(8, 0), (3, 0), (8, 1), (10, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_hessian_accum_activation_views(cuda, dtype, pad, offset):
+    """16-bit activations are read in place through a tensor map when their rows are 16-byte
+    aligned (pad 8, offset 0); a row stride that is not a multiple of 8 elements or a start that is
+    not 16-byte aligned goes through the transposed copy.  Both must give the same Hessian, with
+    ragged token and channel counts."""
+    m, C = 333, 1000
+    g = torch.Generator().manual_seed(17)
+    big = torch.randn(m, C + pad + offset, generator=g).to(dtype)
+    xd = big.to(cuda)[:, offset:offset + C]
+    assert xd.stride(0) == C + pad + offset and xd.stride(1) == 1
+    H0 = synthetic.layer_weight(C, C, 5)
+    H0 = (H0 + H0.t()).contiguous()
+    H = H0.clone().to(cuda)
+    ops.hessian_accum(H, xd, 0.75, 2.0 / m, ops.Precision(math=MATH_TENSOR))
+    x = big[:, offset:offset + C].double()
+    want = 0.75 * H0.double() + (2.0 / m) * (x.t() @ x)
+    Hc = H.cpu()
+    assert float((Hc.double() - want).abs().max() / want.abs().max()) < 5e-6
+    assert torch.equal(Hc, Hc.t())
+
+
 # ------------------------------------------------------------------ prepare
 def test_prepare_golden(cuda, golden):
     H = golden.t("H_final").clone().to(cuda)

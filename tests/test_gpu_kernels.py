@@ -344,6 +344,33 @@ def test_gemm_engine_rank128_update_many_tiles(cuda, beta, upper, N):
     assert torch.equal(got[outside], big[outside]), "elements outside the C window were modified"
 
 
+@pytest.mark.parametrize("M,N,K,upper", [(300, 1000, 200, False), (2048, 256, 96, True), (2048, 256, 300, True), (1000, 1000, 64, True),
+                                         (129, 257, 1000, False), (4000, 4000, 130, True), (1500, 1500, 4096, True)])
+def test_gemm_engine_one_plane_persistent(cuda, M, N, K, upper):
+    """One bf16 plane and N >= 256: the persistent kernel (one CTA per SM walking 128 x 256 tiles).
+    Inputs are bf16-representable, so one plane is exact and the result must agree with float64 to
+    accumulation error; tiles below the diagonal stay untouched with upper_tiles_only, also when the
+    matrix has more rows than columns."""
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).float()
+    B = torch.randn(K, N, generator=g).to(torch.bfloat16).float()
+    C0 = torch.randn(M, N, generator=g)
+    Cd = C0.clone().to(cuda)
+    ops.gemm(A.to(cuda), B.to(cuda), Cd, alpha=0.5, beta=-1.0, upper_tiles_only=upper,
+             precision=ops.Precision(math=MATH_TENSOR), split=1)
+    want = 0.5 * (A.double() @ B.double()) - C0.double()
+    got = Cd.cpu().double()
+    must = torch.ones(M, N, dtype=torch.bool)
+    if upper:
+        # guaranteed: every 128-block on or above the diagonal is computed; nothing below the
+        # diagonal's 256-wide tile is touched (K <= 128 runs in the 128 x 128 panel kernel, larger
+        # K in 128 x 256 tiles, and what lies between the two tilings may be either)
+        must = (torch.arange(N)[None, :] // 128) >= (torch.arange(M)[:, None] // 128)
+        never = ((torch.arange(N)[None, :] // 256) * 256 + 256) <= ((torch.arange(M)[:, None] // 128) * 128)
+        assert torch.equal(got[never], C0.double()[never])
+    assert float((got - want)[must].abs().max() / want.abs().max()) < 5e-6 * max(1.0, K / 256.0)
+
+
 # ------------------------------------------------------------------ inverse-free form of the sweep
 def test_unit_factor_is_inverse_of_reference_factor(cuda, golden, precision):
     H = golden.t("H_damped").clone().to(cuda)

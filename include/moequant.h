@@ -65,26 +65,14 @@ typedef struct {
 int mq_abi_version(void);
 const char* mq_last_error(void);
 
-/* Number of CUDA kernels this library has launched in this process (host-side counter). */
-long long mq_launch_count(void);
-
 /* Every device-side wait in the tensor-core kernels is bounded.  If one ever expires the
  * kernel records a non-zero code, frees its resources and returns; results of that call are
  * then invalid.  This copies the current device's code to *host_out (0 = healthy).  It
  * synchronises the device, so call it where a synchronisation is acceptable.  */
 int mq_engine_fault(int* host_out);
-
-/* Per-kernel timing for benchmarks: between mq_profile_begin() and mq_profile_end() every
- * launch of the kernel families below is bracketed by CUDA events on its own stream.
- * mq_profile_end synchronises the device and fills four arrays of MQ_PROFILE_KINDS entries:
- * launches, summed milliseconds, and two work figures (GEMM kinds: algorithmic flop and
- * issued tensor flop; sweep: algorithmic bytes and flop; split/pack: bytes).
- * Not thread-safe; meant for one benchmarking thread.  */
-#define MQ_PROFILE_KINDS 8
-enum { MQ_PROF_UMMA_GEMM = 0, MQ_PROF_SIMT_GEMM = 1, MQ_PROF_SWEEP_TILE = 2, MQ_PROF_CHOL_DIAG = 3,
-       MQ_PROF_TRSM = 4, MQ_PROF_SPLIT = 5, MQ_PROF_PACK = 6, MQ_PROF_OTHER = 7 };
-int mq_profile_begin(void);
-int mq_profile_end(int64_t* launches, double* milliseconds, double* work, double* work2);
+/* Resets the current device's code to 0 after the caller has dealt with a fault (dropped the
+ * results computed since, checked the device).  Synchronises the device.  */
+int mq_engine_fault_clear(void);
 
 /* ------------------------------------------------------------------ a2
  * H <- beta*H + alpha*X^T X, H (C,C) fp32 symmetric, X (m,C) of x_dtype.
@@ -216,6 +204,15 @@ size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64_t C, int m
  * fp32; zero may be NULL, meaning the symmetric constant (maxq+1)/2.  */
 int mq_dequantize(const uint8_t* codes, int64_t R, int64_t C, const float* scale, const float* zero,
                   int64_t group, int bits, int out_dtype, void* out, void* stream);
+
+/* sum over (r,c) of (A H)[r,c] * A[r,c] for A (R,C) fp32 and H (C,C) fp32, written to *out
+ * (one double on the device).  Numerator (A = q - w) and denominator (A = w) of
+ * get_relative_mse_error (src/quant_utils.py:259-264), the metric quant.py:314-316 logs
+ * after every layer.  workspace: mq_quadratic_form_workspace_bytes(R, C, math, split).  */
+int mq_quadratic_form(const float* A, int64_t R, int64_t C, int64_t lda, const float* H, int64_t ldh,
+                      double* out, int math, int split, void* workspace, size_t workspace_bytes,
+                      void* stream);
+size_t mq_quadratic_form_workspace_bytes(int64_t R, int64_t C, int math, int split);
 
 /* ------------------------------------------------------------------ a11
  * compressed-tensors int4 -> int32 packing of pack_weight / pack_to_int32

@@ -26,6 +26,7 @@ SIGNATURES = {
     "mq_last_error": (c_char_p, []),
     "mq_launch_count": (ctypes.c_longlong, []),
     "mq_engine_fault": (c_int, [ctypes.POINTER(c_int)]),
+    "mq_engine_fault_clear": (c_int, []),
     "mq_profile_begin": (c_int, []),
     "mq_profile_end": (c_int, [ctypes.POINTER(c_int64), ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
                                ctypes.POINTER(ctypes.c_double)]),
@@ -56,6 +57,9 @@ SIGNATURES = {
     "mq_quantize_layer_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int, c_int, c_int]),
     "mq_dequantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                               c_void_p]),
+    "mq_quadratic_form": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,
+                                  c_void_p, c_size_t, c_void_p]),
+    "mq_quadratic_form_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
     "mq_pack_int4": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
 }
 
@@ -87,6 +91,11 @@ def check(status: int) -> None:
     if status != 0:
         msg = lib().mq_last_error().decode(errors="replace")
         raise MoeQuantError(f"mq_status {status}: {msg}")
+
+
+def engine_fault_clear() -> None:
+    """Resets the current device's fault code once the caller has dropped the affected results."""
+    check(lib().mq_engine_fault_clear())
 
 
 def engine_fault() -> int:

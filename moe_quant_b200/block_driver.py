@@ -90,7 +90,7 @@ def quantize_block(
     rel_err: Dict[str, float] = {}
     order: List[str] = []
 
-    def finish(name: str, result) -> None:
+    def finish(name: str, result, main_only: bool) -> None:
         h = handles[name]
         q, s, z = result
         deq = quant_utils.dequantize_linear_weight(q, s, z)
@@ -101,14 +101,16 @@ def quantize_block(
         issues["non_invertible"] += int(h.issue_non_invertible)
         if log_error and not h.has_hessian_issues() and h.H is not None:
             rel_err[name] = float(quant_utils.get_relative_mse_error(deq.float(), h.layer.weight.float(), h.H))
-        if dist_utils.is_main():
+        # shared layers hold the same result on every rank and are written once (quant.py:321);
+        # a routed expert exists on its owner rank only, which writes it itself (quant.py:375-380)
+        if dist_utils.is_main() or not main_only:
             _save(save_dir, f"{prefix}{name}", q, s, z)
         h.layer.weight.data = deq.to(h.layer.weight.dtype).reshape(h.layer.weight.shape)     # quant.py:328
         order.append(name)
 
     # shared layers first, one at a time: they may all-reduce and broadcast (quant.py:295-330)
     for name in shared:
-        finish(name, handles[name].quantize(bits))
+        finish(name, handles[name].quantize(bits), main_only=True)
     for name in shared:
         handles[name].reset()
 
@@ -121,13 +123,13 @@ def quantize_block(
                 gate = name.rsplit(".", 1)[0] + ".gate_proj"
                 if gate in pending:
                     res = quantize_tied([handles[gate], h], bits)
-                    finish(gate, res[0])
-                    finish(name, res[1])
+                    finish(gate, res[0], main_only=False)
+                    finish(name, res[1], main_only=False)
                     pending.remove(gate)
                     pending.remove(name)
     results = quantize_many([handles[n] for n in pending], bits, streams=streams)
     for name, res in zip(pending, results):
-        finish(name, res)
+        finish(name, res, main_only=False)
     for name in experts:
         handles[name].reset()
 

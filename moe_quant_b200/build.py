@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmoequant_sm100.so")
-SOURCES = ["api.cu", "pack.cu", "prepare.cu", "gemm_simt.cu", "hinv.cu", "sweep.cu", "umma_gemm.cu", "profile.cu"]
+SOURCES = ["api.cu", "pack.cu", "prepare.cu", "gemm_simt.cu", "hinv.cu", "sweep.cu", "umma_gemm.cu", "profile.cu", "metrics.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -42,7 +42,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objdir = os.path.join(CSRC, "build")
     os.makedirs(objdir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    headers.append(os.path.join(os.path.dirname(HERE), "include", "moequant.h"))
+    inc = os.path.join(os.path.dirname(HERE), "include")
+    headers += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
 
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))

@@ -37,7 +37,6 @@ size_t hessian_accum_tensor_workspace_bytes(int x_dtype, int64_t m, int64_t C, i
 
 extern "C" int mq_abi_version(void) { return MQ_ABI_VERSION; }
 extern "C" const char* mq_last_error(void) { return mq::g_error; }
-extern "C" long long mq_launch_count(void) { return mq::g_launches; }
 
 // ---------------------------------------------------------------------------- a2
 extern "C" size_t mq_hessian_accum_workspace_bytes(int x_dtype, int64_t m, int64_t C, int math, int split) {

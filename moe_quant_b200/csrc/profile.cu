@@ -1,4 +1,5 @@
 #include "profile.cuh"
+#include "../../include/moequant_bench.h"
 
 #include <vector>
 
@@ -47,6 +48,8 @@ void prof_close(cudaStream_t st) {
 }
 
 }  // namespace mq
+
+extern "C" long long mq_launch_count(void) { return mq::g_launches; }
 
 extern "C" int mq_profile_begin(void) {
   mq::g_profile_on = true;

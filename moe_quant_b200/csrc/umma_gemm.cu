@@ -1352,3 +1352,11 @@ extern "C" int mq_engine_fault(int* host_out) {
   MQ_CUDA(cudaMemcpyFromSymbol(host_out, g_engine_fault, sizeof(int)));
   return MQ_OK;
 }
+
+extern "C" int mq_engine_fault_clear(void) {
+  using namespace mq;
+  const int zero = 0;
+  MQ_CUDA(cudaDeviceSynchronize());
+  MQ_CUDA(cudaMemcpyToSymbol(g_engine_fault, &zero, sizeof(int)));
+  return MQ_OK;
+}

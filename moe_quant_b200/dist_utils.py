@@ -1,11 +1,9 @@
-"""The torch.distributed wrappers that GPTQ and its driver call (src/dist_utils.py:20-65)."""
+"""The torch.distributed queries that the GPTQ handle and the block loop use (src/dist_utils.py:20-41).
+The reference module's parameter broadcast, gather and printing helpers serve its model-loading
+driver, which is not part of this path."""
 from __future__ import annotations
 
-from typing import Any, Optional
-
-import torch
 import torch.distributed as dist
-import torch.nn as nn
 
 
 def is_dist_available_and_initialized() -> bool:
@@ -27,25 +25,3 @@ def is_main() -> bool:
 def barrier(device_ids=None) -> None:
     if is_dist_available_and_initialized():
         dist.barrier(device_ids=device_ids)
-
-
-def broadcast_parameters(module: nn.Module, src: Any = 0, group: Optional[Any] = None) -> None:
-    for param in module.parameters():
-        dist.broadcast(param.data, src=src, group=group)
-
-
-def gather_into_tensor(tensor: torch.Tensor, dim: int = 0):
-    world = get_world_size()
-    out = chunks = None
-    if is_main():
-        shape = list(tensor.shape)
-        shape[dim] *= world
-        out = torch.empty(shape, device=tensor.device, dtype=tensor.dtype)
-        chunks = list(out.chunk(world, dim=dim))
-    dist.gather(tensor, chunks)
-    return out
-
-
-def print_on_main(*args, **kwargs) -> None:
-    if is_main():
-        print(*args, **kwargs)

@@ -23,7 +23,7 @@ import torch.nn as nn
 from torch import Tensor
 from torch.nn.modules.conv import _ConvNd
 
-from . import dist_utils, model_utils, ops
+from . import _lib, dist_utils, model_utils, ops
 from ._lib import MoeQuantError
 
 
@@ -83,11 +83,26 @@ class GPTQ:
     # The NaN / non-invertible checks run on the device.  Their status words are read back
     # only when one of these attributes is looked at, so quantize() itself never blocks the host.
     def _resolve_flags(self) -> None:
+        if not self._pending_flags:
+            return
         for flags in self._pending_flags:
             nan, _dead, _zero, not_pd = flags.tolist()
             self._nan_hessian = self._nan_hessian or bool(nan)
             self._non_invertible = self._non_invertible or bool(not_pd)
+        device = self._pending_flags[0].device
         self._pending_flags = []
+        # The read-back above synchronised with the layer's kernels, so this is the place where an
+        # expired device-side wait of the tensor-core kernels shows: the layer's codes are garbage
+        # then and must not be saved as if they were a result.
+        if device.type == "cuda":
+            with torch.cuda.device(device):
+                code = _lib.engine_fault()
+        else:
+            code = _lib.engine_fault()
+        if code != 0:
+            raise MoeQuantError(
+                f"a tensor-core kernel gave up on a bounded wait (code {code}) on {device}: results computed since "
+                "are invalid; call moe_quant_b200._lib.engine_fault_clear() before reusing the device")
 
     @property
     def issue_nan_hessian(self) -> bool:
@@ -240,28 +255,32 @@ class GPTQ:
         # until the last of them is reset.
         Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
         owner = self.tied_gptq_handle if self.tied_gptq_handle is not None else self
-        if not owner._hessian_ready:
-            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
-            owner._hessian_ready = True
-            self._absorb_flags(flags)
+        self._prepare_shared_hessian(Wf)
         if owner._uhat is None:
             owner._uhat, flags, _ = ops.hinv_upper(self.H.clone(), self.precision)
             self._absorb_flags(flags)
-        self._hessian_ready = True
         scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
         codes, _ = ops.gptq_sweep(Wf, owner._uhat, scale, None, g, self.d_col // g, 1, bits, self.W_dtype,
                                   precision=self.precision)
         return codes, scale
+
+    def _prepare_shared_hessian(self, Wf: Tensor) -> None:
+        """Masks and damps H exactly once per Hessian: the handle that owns it keeps the flag, and a
+        tied handle finds the work done (the reference skips the regularisation for tied handles,
+        src/gptq.py:227)."""
+        owner = self.tied_gptq_handle if self.tied_gptq_handle is not None else self
+        if not owner._hessian_ready:
+            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
+            owner._hessian_ready = True
+            self._absorb_flags(flags)
+        self._hessian_ready = True
 
     def _quantize_act_order(self, bits: int, g: int) -> Tuple[Tensor, Tensor]:
         """Activation ordering (src/gptq.py:180-187): columns sorted by decreasing diag(H); each
         column keeps the scale of its original group."""
         W = self._weight_2d()
         Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
-        if not self._hessian_ready:
-            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
-            self._hessian_ready = True
-            self._absorb_flags(flags)
+        self._prepare_shared_hessian(Wf)
         scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
         perm = torch.argsort(self.H.diag(), descending=True)
         Hp = self.H[perm][:, perm].contiguous()
@@ -282,10 +301,7 @@ class GPTQ:
     def _get_hessian_inverse(self) -> Tensor:
         """Seam of src/gptq.py:220-243: mask, damp (once per Hessian) and factor."""
         Wf = self._weight_2d().float().contiguous()
-        if not self._hessian_ready:
-            flags = ops.hessian_prepare(self.H, Wf, self.rel_damp)
-            self._hessian_ready = True
-            self._absorb_flags(flags)
+        self._prepare_shared_hessian(Wf)
         U, flags, _ = ops.hinv_upper(self.H.clone(), self.precision)
         self._absorb_flags(flags)
         return U

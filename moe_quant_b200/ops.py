@@ -252,6 +252,25 @@ def dequantize(codes: Tensor, scale: Tensor, zero: Optional[Tensor], group: int,
     return out
 
 
+def quadratic_form(A: Tensor, H: Tensor, precision: Optional[Precision] = None) -> Tensor:
+    """sum((A @ H) * A) as a 0-d float64 tensor on the device.  A (R, C) fp32, H (C, C) fp32."""
+    p = _prec(precision)
+    require_cuda(A, "A")
+    require_cuda(H, "H")
+    if A.dtype != torch.float32 or H.dtype != torch.float32 or A.dim() != 2 or H.shape != (A.shape[1], A.shape[1]):
+        raise MoeQuantError("quadratic_form: A must be (R, C) fp32 and H (C, C) fp32")
+    A = A if A.stride(1) == 1 else A.contiguous()
+    H = H if H.stride(1) == 1 else H.contiguous()
+    R, C = A.shape
+    out = torch.empty((), dtype=torch.float64, device=A.device)
+    L = lib()
+    ws = _lib.workspace(A.device, L.mq_quadratic_form_workspace_bytes(R, C, p.math, p.split_hinv))
+    with torch.cuda.device(A.device):
+        check(L.mq_quadratic_form(ptr(A), R, C, A.stride(0), ptr(H), H.stride(0), ptr(out), p.math, p.split_hinv,
+                                  ptr(ws), ws.numel(), stream_ptr(A.device)))
+    return out
+
+
 def pack_int4(codes: Tensor, zero_i8: Optional[Tensor] = None, group: int = 0) -> Tensor:
     """(R, C) uint8 codes -> (R, ceil(C/8)) int32 words in the compressed-tensors layout."""
     require_cuda(codes, "codes")

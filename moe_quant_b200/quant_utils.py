@@ -58,8 +58,13 @@ def dequantize_linear_weight(qweight: Tensor, scale: Tensor, zero: Tensor, perm:
 
 
 def get_relative_mse_error(q: Tensor, w: Tensor, H: Optional[Tensor] = None) -> Tensor:
-    """src/quant_utils.py:259-264; two plain library GEMMs, a logging metric."""
-    delta = q - w
+    """mean((q-w) H o (q-w)) / (mean(w H o w) + 1e-6) (src/quant_utils.py:259-264).  Both
+    quadratic forms run on the engine (`mq_quadratic_form`); the result is an fp32 scalar on the
+    device like the reference's."""
+    delta = (q - w).float()
     if H is None:
         return delta.pow(2).mean() / w.pow(2).mean()
-    return delta.mm(H).mul(delta).mean() / (w.mm(H).mul(w).mean() + 1e-6)
+    n = float(w.numel())
+    num = ops.quadratic_form(delta, H.float()) / n
+    den = ops.quadratic_form(w.float(), H.float()) / n
+    return (num / (den + 1e-6)).float()

@@ -12,10 +12,18 @@ from moe_quant_b200._lib import MoeQuantError
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "moequant.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mq_[a-z0-9_]+)\s*\(", text)))
+def _declared_symbols(headers=("moequant.h", "moequant_bench.h")):
+    names = set()
+    for header in headers:
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(mq_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_product_header_holds_no_measurement_hooks():
+    product = _declared_symbols(("moequant.h",))
+    assert not [n for n in product if "profile" in n or "launch_count" in n]
 
 
 def test_library_exports_every_declared_symbol():

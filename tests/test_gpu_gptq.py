@@ -135,6 +135,46 @@ def test_activation_order(cuda, precision):
     _check_against(q, s, z, W, want["qweight"], want["scale"], H_raw, torch.bfloat16, 128)
 
 
+def test_tied_handles_with_activation_order(cuda, precision):
+    """gate_proj / up_proj tied under activation ordering: the shared Hessian is regularised once
+    (by its owner), whichever handle is quantized first and through whichever call."""
+    R, C, N = 48, 512, 700
+    Wg = synthetic.layer_weight(R, C, 31, torch.bfloat16)
+    Wu = synthetic.layer_weight(R, C, 32, torch.bfloat16)
+    X = synthetic.activations(N, C, 33, torch.bfloat16)
+    H_raw, _ = O.hessian_update(None, 0, X)
+    want_g = O.quantize_layer(Wg, H_raw.clone(), bits=4, group_size=128, block_size=128, act_order=True)
+    want_u = O.quantize_layer(Wu, H_raw.clone(), bits=4, group_size=128, block_size=128, act_order=True)
+    damped = H_raw + 1e-2 * torch.diag(H_raw).mean() * torch.eye(C)
+
+    def handles():
+        gate = GPTQ(_layer(Wg, cuda), 128, True, 1e-2, 128, "activation", precision=precision)
+        up = GPTQ(_layer(Wu, cuda), 128, True, 1e-2, 128, "activation", tied_gptq_handle=gate, precision=precision)
+        gate.update(X.to(cuda))
+        return gate, up
+
+    gate, up = handles()
+    qg, sg, zg = gate.quantize(4)
+    qu, su, zu = up.quantize(4)
+    torch.testing.assert_close(gate.H.cpu(), damped, rtol=2e-5, atol=1e-6)      # damped once, not twice
+    _check_against(qg, sg, zg, Wg, want_g["qweight"], want_g["scale"], H_raw, torch.bfloat16, 128)
+    _check_against(qu, su, zu, Wu, want_u["qweight"], want_u["scale"], H_raw, torch.bfloat16, 128)
+    gate, up = handles()
+    (qg2, _, _), (qu2, _, _) = quantize_tied([gate, up], 4)      # falls back to one call per handle
+    torch.testing.assert_close(gate.H.cpu(), damped, rtol=2e-5, atol=1e-6)
+    assert torch.equal(qg2, qg) and torch.equal(qu2, qu)
+    # the Hessian-inverse seam of a tied handle must not regularise again either
+    up._get_hessian_inverse()
+    torch.testing.assert_close(gate.H.cpu(), damped, rtol=2e-5, atol=1e-6)
+
+
+def test_engine_fault_clear_leaves_a_healthy_device_healthy(cuda):
+    from moe_quant_b200 import _lib
+    assert _lib.engine_fault() == 0
+    _lib.engine_fault_clear()
+    assert _lib.engine_fault() == 0
+
+
 def test_full_size_layer_properties(cuda, precision):
     """2048 x 7168 (the expert gate_proj shape): too large for the oracle to finish in
     seconds, so check what must hold at any size: codes in range, finite dequantized
@@ -202,4 +242,4 @@ def test_conv_layer_goes_through_unfold(cuda, precision):
     H, _ = O.hessian_update(None, 0, patches)
     want = O.quantize_layer(conv.weight.detach().cpu().flatten(1), H, bits=4, group_size=32, rel_damp=1e-2, block_size=128)
     assert torch.equal(s.cpu().float(), want["scale"].float())
-    assert O.code_agreement(q.cpu(), want["qweight"]) >= 0.99
+    assert O.code_agreement(q.cpu(), want["qweight"]) >= CODE_AGREEMENT

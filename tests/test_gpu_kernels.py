@@ -84,6 +84,24 @@ def test_dequantize_golden(cuda, golden):
     assert torch.equal(got2.float(), got.float())
 
 
+def test_relative_error_golden(cuda, golden, precision):
+    """get_relative_mse_error on the engine against the number the reference's own function
+    returned for the fixture (src/quant_utils.py:259-264)."""
+    from moe_quant_b200 import quant_utils
+    ops.set_default_precision(precision)
+    try:
+        deq = golden.t("dequantized", typed=True).float().to(cuda)
+        rel = quant_utils.get_relative_mse_error(deq, golden.W.float().to(cuda), golden.t("H_damped").to(cuda))
+    finally:
+        ops.set_default_precision(ops.Precision())
+    want = float(golden.t("rel_error"))
+    assert rel.dtype == torch.float32 and rel.dim() == 0
+    assert abs(float(rel) - want) <= 2e-4 * want
+    plain = quant_utils.get_relative_mse_error(deq, golden.W.float().to(cuda))
+    d = deq.cpu() - golden.W.float()
+    assert abs(float(plain) - float(d.pow(2).mean() / golden.W.float().pow(2).mean())) <= 1e-5 * float(plain)
+
+
 # ------------------------------------------------------------------ Hessian
 def test_hessian_accum_golden(cuda, golden, precision):
     C = golden.W.shape[1]

@@ -66,3 +66,19 @@ def test_model_utils():
     got = model_utils.select_layers(model, "", ".*", model_utils.LINEAR_LAYERS)
     assert sorted(got) == ["0", "2.0"]
     assert sorted(model_utils.select_layers(model, "2", ".*", nn.Linear)) == ["2.0"]
+
+
+def test_expired_device_wait_is_reported_with_the_layer_flags(monkeypatch):
+    """Reading a layer's status words is where an expired wait of the tensor-core kernels must
+    surface: the codes of that layer are garbage and may not be saved as a result."""
+    from moe_quant_b200 import _lib
+
+    h = GPTQ(_layer(), 8, True)
+    h._pending_flags = [torch.zeros(4, dtype=torch.int32)]
+    monkeypatch.setattr(_lib, "engine_fault", lambda: 13)
+    with pytest.raises(MoeQuantError, match="bounded wait"):
+        h.has_hessian_issues()
+    # once reported, the flags are consumed; a healthy device reads clean again
+    monkeypatch.setattr(_lib, "engine_fault", lambda: 0)
+    h._pending_flags = [torch.tensor([1, 0, 0, 5], dtype=torch.int32)]
+    assert h.issue_nan_hessian and h.issue_non_invertible

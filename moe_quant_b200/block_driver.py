@@ -19,7 +19,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import dist_utils, model_utils, quant_utils
-from .gptq import GPTQ, quantize_many, quantize_tied
+from .gptq import GPTQ, quantize_many, quantize_shared, quantize_tied
 
 ROUTED_EXPERTS_REGEX = r".*mlp\.experts\.\d+\.(down|gate|up)_proj$"   # quant.py:24
 
@@ -90,7 +90,7 @@ def quantize_block(
     rel_err: Dict[str, float] = {}
     order: List[str] = []
 
-    def finish(name: str, result, main_only: bool) -> None:
+    def finish(name: str, result, main_only: bool, error: Optional[float] = None) -> None:
         h = handles[name]
         q, s, z = result
         deq = quant_utils.dequantize_linear_weight(q, s, z)
@@ -99,7 +99,9 @@ def quantize_block(
         issues["zero_samples"] += int(h.issue_zero_samples)
         issues["nan_hessian"] += int(h.issue_nan_hessian)
         issues["non_invertible"] += int(h.issue_non_invertible)
-        if log_error and not h.has_hessian_issues() and h.H is not None:
+        if log_error and error is not None:
+            rel_err[name] = error
+        elif log_error and main_only is False and not h.has_hessian_issues() and h.H is not None:
             rel_err[name] = float(quant_utils.get_relative_mse_error(deq.float(), h.layer.weight.float(), h.H))
         # shared layers hold the same result on every rank and are written once (quant.py:321);
         # a routed expert exists on its owner rank only, which writes it itself (quant.py:375-380)
@@ -108,9 +110,13 @@ def quantize_block(
         h.layer.weight.data = deq.to(h.layer.weight.dtype).reshape(h.layer.weight.shape)     # quant.py:328
         order.append(name)
 
-    # shared layers first, one at a time: they may all-reduce and broadcast (quant.py:295-330)
-    for name in shared:
-        finish(name, handles[name].quantize(bits), main_only=True)
+    # shared layers first (quant.py:295-330).  With several ranks each layer's Hessian is reduced
+    # to an owner rank, owners quantize side by side and broadcast (gptq.quantize_shared); the
+    # reference lets rank 0 do them one after the other.
+    shared_out = quantize_shared([handles[n] for n in shared], bits, streams=streams, want_error=log_error)
+    shared_results, shared_errors = shared_out if log_error else (shared_out, [None] * len(shared))
+    for name, res, err in zip(shared, shared_results, shared_errors):
+        finish(name, res, main_only=True, error=err)
     for name in shared:
         handles[name].reset()
 

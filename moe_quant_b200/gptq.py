@@ -382,3 +382,165 @@ def quantize_tied(handles: Sequence[GPTQ], bits: int) -> List[Tuple[Tensor, Tens
                 dist.broadcast(t, src=0)
         out.append((q, s, z))
     return out
+
+
+def shared_layer_owners(handles: Sequence[GPTQ], world: int) -> List[int]:
+    """Rank that quantizes each distributed handle.  Handles are dealt out by estimated cost
+    (factorisation 2/3 C^3 plus sweep R C^2 flop), largest first, each to the rank with the least
+    work so far; a tied handle goes where the handle that owns its Hessian goes.  Depends only on
+    shapes and order, so every rank computes the same table."""
+    n = len(handles)
+    index = {id(h): i for i, h in enumerate(handles)}
+    cost = [0.0] * n
+    for i, h in enumerate(handles):
+        root = index.get(id(h.tied_gptq_handle), i) if h.tied_gptq_handle is not None else i
+        c = float(h.d_col)
+        cost[root] += (0.0 if root != i else 2.0 / 3.0 * c ** 3) + float(h.d_row) * c * c
+    owner = [-1] * n
+    load = [0.0] * world
+    for i in sorted((i for i in range(n) if cost[i] > 0.0 or handles[i].tied_gptq_handle is None), key=lambda i: (-cost[i], i)):
+        if handles[i].tied_gptq_handle is not None and id(handles[i].tied_gptq_handle) in index:
+            continue
+        r = min(range(world), key=lambda k: (load[k], k))
+        owner[i] = r
+        load[r] += cost[i]
+    for i, h in enumerate(handles):
+        if owner[i] < 0:
+            owner[i] = owner[index[id(h.tied_gptq_handle)]] if id(h.tied_gptq_handle) in index else 0
+    return owner
+
+
+@torch.no_grad()
+def quantize_shared(handles: Sequence[GPTQ], bits: int, streams: int = 4, want_error: bool = False):
+    """Quantizes the distributed handles of a block (attention projections, shared experts, dense
+    MLPs: the layers every rank sees tokens for) with every rank working.
+
+    The reference all-reduces each Hessian, lets rank 0 quantize one layer after the other while
+    the other ranks wait, and broadcasts each result (src/gptq.py:138-139, 167-212).  Here each
+    layer has an owner rank (`shared_layer_owners`): its Hessian is REDUCED to the owner with
+    token-count weights, owners quantize their layers side by side, and every result is broadcast
+    from its owner, so all ranks end with identical (qweight, scale, zero) as the reference
+    requires.  The five MLA projections of a DeepSeek block then cost about as much as the
+    largest of them instead of their sum.
+
+    Returns [(qweight, scale, zero)] in the order of `handles`; with want_error also the list of
+    get_relative_mse_error values (computed by the owner against the reduced, damped Hessian, as
+    rank 0 does in quant.py:314-316; None where the Hessian had an issue).
+    The issue flags of every handle are set on every rank.
+    """
+    handles = list(handles)
+    bits = int(bits)
+    if not (dist_utils.is_dist_available_and_initialized() and dist_utils.get_world_size() > 1):
+        out = [h.quantize(bits) for h in handles]
+        return (out, [_relative_error(h, r) for h, r in zip(handles, out)]) if want_error else out
+    world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
+    owners = shared_layer_owners(handles, world)
+    device = handles[0].W_device
+    roots = [i for i, h in enumerate(handles) if h.tied_gptq_handle is None]
+
+    # ---- Hessians to their owners, weighted by token counts (ranks may hold different numbers)
+    counts = torch.tensor([float(handles[i].num_samples if handles[i].H is not None else 0) for i in roots],
+                          dtype=torch.float64, device=device)
+    totals = counts.clone()
+    dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    for k, i in enumerate(roots):
+        h = handles[i]
+        total = float(totals[k].item())
+        if total == 0.0:                       # nobody saw a token: identity Hessian (src/gptq.py:129-136)
+            h.H = None
+            continue
+        if h.H is None:
+            h.H = torch.zeros(h.d_col, h.d_col, device=device, dtype=torch.float32)
+        else:
+            h.H.mul_(h.num_samples / total)
+        dist.reduce(h.H, dst=owners[i], op=dist.ReduceOp.SUM)
+        h.num_samples = int(total)
+    for h in handles:
+        was_distributed, h.is_distributed = h.is_distributed, False     # the collectives are done here
+        try:
+            h.quantization_pre_step()
+        finally:
+            h.is_distributed = was_distributed
+
+    # ---- owners quantize what they own, groups that share a Hessian with one factorisation
+    mine = [i for i in range(len(handles)) if owners[i] == rank]
+    results: List[Optional[Tuple[Tensor, Tensor, Tensor]]] = [None] * len(handles)
+    groups: List[List[int]] = []
+    for i in mine:
+        h = handles[i]
+        if h.tied_gptq_handle is None:
+            groups.append([i] + [j for j in mine if handles[j].tied_gptq_handle is h])
+        elif not any(h.tied_gptq_handle is handles[j] for j in mine):
+            groups.append([i])
+    if groups:
+        current = torch.cuda.current_stream(device) if device.type == "cuda" else None
+        pool = _side_streams(device, max(1, min(streams, len(groups)))) if current is not None else [None]
+        for s in pool:
+            if s is not None:
+                s.wait_stream(current)
+        for k, grp in enumerate(groups):
+            s = pool[k % len(pool)]
+            ctx = torch.cuda.stream(s) if s is not None else _NullContext()
+            with ctx:
+                hs = [handles[i] for i in grp]
+                flags = [h.is_distributed for h in hs]
+                for h in hs:
+                    h.is_distributed = False
+                try:
+                    res = quantize_tied(hs, bits) if len(hs) > 1 else [hs[0]._quantize(bits)]
+                finally:
+                    for h, f in zip(hs, flags):
+                        h.is_distributed = f
+                for i, r in zip(grp, res):
+                    results[i] = r
+        if current is not None:
+            for s in pool:
+                current.wait_stream(s)
+            for i in mine:
+                for t in results[i]:
+                    t.record_stream(current)
+
+    # ---- status and error metric of every layer, then the results, from their owners
+    errors: List[Optional[float]] = [None] * len(handles)
+    status = torch.zeros(len(handles), 4, dtype=torch.float64, device=device)
+    for i in mine:
+        h = handles[i]
+        status[i, 0], status[i, 1], status[i, 2] = float(h.issue_zero_samples), float(h.issue_nan_hessian), float(h.issue_non_invertible)
+        if want_error:
+            e = _relative_error(h, results[i])
+            status[i, 3] = float("nan") if e is None else e
+    dist.all_reduce(status, op=dist.ReduceOp.SUM)          # every row has exactly one writer
+    status = status.cpu()
+    pending = []
+    for i, h in enumerate(handles):
+        h.issue_zero_samples = bool(status[i, 0])
+        h._nan_hessian, h._non_invertible = bool(status[i, 1]), bool(status[i, 2])
+        e = float(status[i, 3])
+        errors[i] = None if (e != e or not want_error) else e
+        if results[i] is None:
+            g = h._group()
+            results[i] = (torch.empty(h.d_row, h.d_col, device=device, dtype=torch.uint8),
+                          torch.empty(h.d_row, h.d_col // g, device=device, dtype=h.W_dtype),
+                          torch.empty(h.d_row, h.d_col // g, device=device, dtype=h.W_dtype))
+        for t in results[i]:
+            pending.append(dist.broadcast(t, src=owners[i], async_op=True))
+    for work in pending:
+        work.wait()
+    return (results, errors) if want_error else results
+
+
+def _relative_error(h: GPTQ, result) -> Optional[float]:
+    from . import quant_utils
+    if h.has_hessian_issues() or h.H is None:
+        return None
+    q, s, z = result
+    deq = quant_utils.dequantize_linear_weight(q, s, z)
+    return float(quant_utils.get_relative_mse_error(deq.float(), h._weight_2d().float(), h.H))
+
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

@@ -2,6 +2,7 @@
 """GPTQ layers/sec on the DeepSeek-V3 routed-expert gate_proj shape (2048 x 7168, 4 bit, g128).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --workload {all,headline,down_proj,mla,moe_layer}
     python bench.py --single-layer --steps 1        (small untimed case for profiler captures)
 
 One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1).  Routed experts
@@ -10,17 +11,22 @@ job is weak-scaled and `value` is (layers all ranks quantized) / (max-over-ranks
 
 A step is one `GPTQ.quantize(4)` call on one expert's gate_proj whose Hessian is already
 accumulated on the device: pre-step, scales, Hessian-inverse factor, column sweep, codes out.
-Steps rotate over distinct experts (weight 29 MB + Hessian 205 MB each, larger than L2).
+Steps rotate over distinct experts (weight 29 MB + Hessian 205 MB each, larger than L2).  The
+pass of K steps is timed `--reps` times (default 5); `value` is K / (median pass time).
 
 Printed JSON (one line, rank 0):
   value      layers/s with inputs resident in HBM
-  e2e        layers/s through the public handle with HOST buffers: weight and calibration
-             activations copied from pinned memory, Hessian accumulated, layer quantized,
-             codes and scales copied back, every step
-  roofline   the kernel that takes the largest share of a step, timed with CUDA events on
-             its launching stream by the library's profiling hooks in a separate pass
+  e2e        layers/s through the public handles with HOST buffers: per expert the calibration
+             activations and the gate_proj / up_proj weights are copied from pinned memory, the
+             Hessian is accumulated, both layers are quantized, codes and scales copied back
+  roofline   the kernel family that takes the largest share of a step, timed with CUDA events on
+             its launching stream by the library's measurement hooks in a separate pass
+  parity     code agreement of one sampled step with the CPU oracle on a slice of rows (untimed)
   cpu_baseline  the CPU oracle (a port of the reference's torch path) on this box's cores
-`--impl reference` times that CPU path alone, as the reference arm.
+  extra      the other named workloads (`--workload all`, the default): expert down_proj with the
+             group-size sweep and packing, the five MLA projections, one rank's shard of a whole
+             MoE layer including its ragged Hessian accumulation
+`--impl reference` times the CPU path alone, as the reference arm.
 """
 from __future__ import annotations
 
@@ -28,7 +34,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 
@@ -40,6 +45,8 @@ sys.path.insert(0, ROOT)
 R, C, TOKENS, GROUP, BITS = 2048, 7168, 4096, 128, 4
 WORKLOAD = "deepseek_v3_routed_expert_gate_proj_2048x7168_bf16_g128 (one rank's expert shard, Hessian resident)"
 METRIC = "GPTQ layers/sec (2048x7168, 4b g128)"
+CONFIG = {"workload": WORKLOAD, "rows": R, "cols": C, "bits": BITS, "group_size": GROUP, "rel_damp": 1e-2,
+          "weight_dtype": "bf16", "calibration_tokens_mean": TOKENS}
 
 
 def _peaks():
@@ -52,6 +59,12 @@ def _peaks():
     return dict(hbm=6650.0, tensor_burst=1590.0, tensor_sustained=1400.0, source="fallback")
 
 
+def layer_flop(rows: int, cols: int, block: int = 128) -> float:
+    """fp32-equivalent flop of one GPTQ.quantize in the reference's formulation: potrf + potri +
+    potrf are replaced by their useful part 2/3 C^3, plus the lazy and in-block updates."""
+    return 2.0 / 3.0 * cols ** 3 + float(rows) * cols * (cols - block) + float(rows) * cols * (block - 1)
+
+
 class ClockSampler:
     """SM clock and throttle reasons of one GPU while the timed region runs, read through NVML
     (the source nvidia-smi prints) from a thread of this process.  NVML is initialised when the
@@ -60,7 +73,7 @@ class ClockSampler:
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.01):
         import threading
         self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         self.samples, self.recording, self.period = [], False, period_s
@@ -159,9 +172,10 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "layers/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": "one full 2048x7168 layer per step, Hessian from 4096 tokens"},
+        "config": dict(CONFIG),
         "cpu_baseline": {"value": value, "unit": "layers/s", "cores": cores, "kind": "port",
-                         "sample": f"{steps} full layers after {warmup} warm-up, torch CPU oracle, {cores} threads"},
+                         "sample": f"{steps} full 2048x7168 layers after {warmup} warm-up, Hessian from {TOKENS} tokens "
+                                   f"accumulated beforehand, torch CPU port of the reference path, {cores} threads"},
         "hessian_tflops_2nc2_cpu": h_tflops,
         "e2e": {"value": value, "unit": "layers/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -169,9 +183,34 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------- B200 arm
+class Ctx:
+    pass
+
+
+def _event_pair():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _randn_acts(tokens, cols, dtype, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    chan = torch.exp(torch.randn(cols, generator=g, device=dev))
+    return (torch.randn(tokens, cols, generator=g, device=dev) * chan).to(dtype)
+
+
+def _randn_weight(rows, cols, dtype, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return (0.02 * torch.randn(rows, cols, generator=g, device=dev)).to(dtype)
+
+
+def _linear(W):
+    import torch.nn as nn
+    layer = nn.Linear(W.shape[1], W.shape[0], bias=False, dtype=W.dtype, device="meta")
+    layer.weight = nn.Parameter(W, requires_grad=False)
+    return layer
+
+
 def run_b200(args):
     import torch.distributed as dist
-    import torch.nn as nn
 
     from moe_quant_b200 import GPTQ, _lib, ops, quantize_many, synthetic
 
@@ -183,47 +222,96 @@ def run_b200(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    steps, warmup = args.steps, max(args.warmup, 3)
-    clocks = ClockSampler(local)         # NVML comes up here, not beside the timed region
+    cx = Ctx()
+    cx.world, cx.rank, cx.dev, cx.dist = world, rank, dev, dist
+    cx.steps, cx.warmup, cx.reps = args.steps, max(args.warmup, 3), max(1, args.reps)
+    cx.n_streams = max(1, args.streams)
+    cx.clocks = ClockSampler(local)         # NVML comes up here, not beside the timed region
+    cx.peaks = _peaks()
+    cx.seed = 1234 + 100 * rank
     n_experts = 4
-    seed = 1234 + 100 * rank
-
-    # ---- this rank's experts: weights and Hessians resident in HBM (set-up, untimed)
-    counts = synthetic.ragged_expert_counts(32 * 1024, 256, 8, seed)   # ragged top-8 routing of 32k tokens
-    weights, hessians, tokens = [], [], []
-    for e in range(n_experts):
-        W = synthetic.layer_weight(R, C, seed + e, torch.bfloat16).to(dev)
-        m = int(counts[(rank * n_experts + e) % 256].clamp(min=256, max=4 * TOKENS))
-        g = torch.Generator(device=dev).manual_seed(seed + e)
-        chan = torch.exp(torch.randn(C, generator=g, device=dev))
-        X = (torch.randn(m, C, generator=g, device=dev) * chan).to(torch.bfloat16)
-        H = torch.zeros(C, C, dtype=torch.float32, device=dev)
-        ops.hessian_accum(H, X, 0.0, 2.0 / m)
-        weights.append(W)
-        hessians.append(H)
-        tokens.append(m)
-        del X
-
-    def make_handles(n):
-        hs = []
-        for i in range(n):
-            e = i % n_experts
-            layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
-            layer.weight = nn.Parameter(weights[e], requires_grad=False)
-            h = GPTQ(layer, GROUP, True, 1e-2, 128)
-            h.H = hessians[e].clone()
-            h.num_samples = tokens[e]
-            hs.append(h)
-        return hs
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    cx.barrier = barrier
+
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    cx.max_over_ranks = max_over_ranks
+
+    # ---- this rank's experts: weights and Hessians resident in HBM (set-up, untimed)
+    counts = synthetic.ragged_expert_counts(32 * 1024, 256, 8, cx.seed)   # ragged top-8 routing of 32k tokens
+    weights, hessians, tokens = [], [], []
+    for e in range(n_experts):
+        W = synthetic.layer_weight(R, C, cx.seed + e, torch.bfloat16).to(dev)
+        m = int(counts[(rank * n_experts + e) % 256].clamp(min=256, max=4 * TOKENS))
+        X = _randn_acts(m, C, torch.bfloat16, cx.seed + e, dev)
+        H = torch.zeros(C, C, dtype=torch.float32, device=dev)
+        ops.hessian_accum(H, X, 0.0, 2.0 / m)
+        weights.append(W)
+        hessians.append(H)
+        tokens.append(m)
+        del X
+    cx.weights, cx.hessians, cx.tokens, cx.n_experts = weights, hessians, tokens, n_experts
+
+    def make_handles(n):
+        hs = []
+        for i in range(n):
+            e = i % n_experts
+            h = GPTQ(_linear(weights[e]), GROUP, True, 1e-2, 128)
+            h.H = hessians[e].clone()
+            h.num_samples = tokens[e]
+            hs.append(h)
+        return hs
+
+    cx.make_handles = make_handles
+    want = args.workload
+    line = {}
+    if want in ("all", "headline"):
+        line = headline(cx)
+    extra = {}
+    if want in ("all", "down_proj") and rank == 0:
+        extra["down_proj"] = _guarded(wl_down_proj, cx)
+    if want in ("all", "moe_layer"):
+        extra["moe_layer"] = _guarded(wl_moe_layer, cx)
+    if want in ("all", "mla"):
+        extra["mla"] = wl_mla(cx)                 # collectives inside: every rank must take part, no guard
+    cx.clocks.close()
+    if rank == 0:
+        if not line:
+            line = {"metric": METRIC, "value": None, "unit": "layers/s", "n_gpus": world, "config": dict(CONFIG)}
+        line["extra"] = extra
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _guarded(fn, cx):
+    try:
+        return fn(cx)
+    except Exception as exc:  # noqa: BLE001 - an extra workload must not take the headline down with it
+        torch.cuda.synchronize()
+        return {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def headline(cx):
+    import torch.nn as nn
+
+    from moe_quant_b200 import GPTQ, _lib, ops, quantize_many, quantize_tied, synthetic
+
+    dev, world, rank = cx.dev, cx.world, cx.rank
+    steps, n_streams, barrier = cx.steps, cx.n_streams, cx.barrier
+    make_handles = cx.make_handles
+
     # ---- timed region: K quantize() calls, issued round-robin on `streams` CUDA streams
-    # (independent experts: their kernel chains overlap on the GPU)
-    n_streams = max(1, args.streams)
+    # (independent experts: their kernel chains overlap on the GPU).
     # The warm-up is a whole pass of the same length with its results kept, then dropped: every
     # stream of the pool gets its workspace, and the caching allocator's per-stream pools hold
     # every block the timed pass will ask for.  A cudaMalloc inside the timed region goes
@@ -235,86 +323,97 @@ def run_b200(args):
     # and anything up to a few hundred steps is one chunk.
     free_bytes, _total = torch.cuda.mem_get_info(dev)
     chunk = max(n_streams, min(steps, int(0.6 * free_bytes / 225e6)))
-    warmup = max(warmup, min(steps, chunk))
-    pre = make_handles(min(warmup, chunk))
+    pre = make_handles(min(max(cx.warmup, steps), chunk))
     pre_results = quantize_many(pre, BITS, streams=n_streams)
     barrier()
     del pre, pre_results
-    launches0 = _lib.lib().mq_launch_count()
-    ms_total, done, issues = 0.0, 0, 0
-    while done < steps:
-        n = min(chunk, steps - done)
-        handles = make_handles(n)
-        barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with clocks:
-            ev0.record()
-            results = quantize_many(handles, BITS, streams=n_streams)
-            ev1.record()
+
+    def timed_pass():
+        ms_total, done, issues = 0.0, 0, 0
+        while done < steps:
+            n = min(chunk, steps - done)
+            handles = make_handles(n)
             barrier()
-        ms_total += ev0.elapsed_time(ev1)
-        issues += sum(h.has_hessian_issues() for h in handles)
-        done += n
-        del handles, results
-    clocks.close()
-    launches = _lib.lib().mq_launch_count() - launches0
+            ev0, ev1 = _event_pair()
+            with cx.clocks:
+                ev0.record()
+                results = quantize_many(handles, BITS, streams=n_streams)
+                ev1.record()
+                barrier()
+            ms_total += ev0.elapsed_time(ev1)
+            issues += sum(h.has_hessian_issues() for h in handles)
+            done += n
+            del handles, results
+        return cx.max_over_ranks(ms_total), issues
+
+    launches0 = _lib.lib().mq_launch_count()
+    passes, issues = [], 0
+    for _ in range(cx.reps):
+        ms, bad = timed_pass()
+        passes.append(ms)
+        issues += bad
+    launches = (_lib.lib().mq_launch_count() - launches0) // cx.reps
+    ms_med = statistics.median(passes)
+    value = world * steps / (ms_med / 1e3)
+
     steps_aux = min(steps, 48)             # the secondary rates below are measured on at most 48 steps
     # the same K calls one after the other on one stream (what a plain `for handle: quantize` loop gets)
     seq_pre = make_handles(steps_aux)      # same untimed pass first, for the same reason
     seq_pre_results = [h.quantize(BITS) for h in seq_pre]
     barrier()
     del seq_pre, seq_pre_results
-    seq_handles = make_handles(steps_aux)
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    seq_results = [h.quantize(BITS) for h in seq_handles]
-    s1.record()
-    barrier()
-    ms_single = s0.elapsed_time(s1)
-    del seq_handles, seq_results
+    seq_ms = []
+    for _ in range(min(cx.reps, 3)):
+        seq_handles = make_handles(steps_aux)
+        barrier()
+        s0, s1 = _event_pair()
+        s0.record()
+        seq_results = [h.quantize(BITS) for h in seq_handles]
+        s1.record()
+        barrier()
+        seq_ms.append(s0.elapsed_time(s1))
+        del seq_handles, seq_results
+    ms_single = statistics.median(seq_ms)
     fault = _lib.engine_fault()
-
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    value = world * steps / (ms_max / 1e3)
 
     # ---- per-kernel pass (same work, events around every launch of the hot kernels), on one stream
     # directly after the one-stream pass: the library then sizes its grids as for a single caller
-    prof_handles = make_handles(min(steps, 4))
+    n_prof = min(steps, 4)
+    prof_handles = make_handles(n_prof)
     torch.cuda.synchronize()
     _lib.profile_begin()
     for h in prof_handles:
         h.quantize(BITS)
     prof = _lib.profile_end()
     del prof_handles
-    peaks = _peaks()
+    peaks = cx.peaks
     kinds = {k: v for k, v in prof.items() if v["launches"]}
     top = max(kinds, key=lambda k: kinds[k]["ms"]) if kinds else None
-    roofline, shares = None, {}
+    roofline, shares, per_layer_us = None, {}, {}
     if top:
         tot = sum(v["ms"] for v in kinds.values())
         shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
+        per_layer_us = {k: round(v["ms"] / n_prof * 1e3, 1) for k, v in kinds.items()}
         v = kinds[top]
         if top in ("umma_gemm", "simt_gemm"):
             secs = v["ms"] / 1e3
             products = 6.0 if top == "umma_gemm" else 1.0     # bf16 products per fp32 product with three planes
             achieved = v["work"] * products / secs / 1e12
-            # DRAM bytes per 128x128 output tile of a rank-128 update from the committed ncu capture
-            # (141.1 MB for 1485 tiles, profiles/umma_panel_kernel_trailing_update_7168.md); traffic
-            # grows with the tile count, so the average launch is scaled by its tiles
-            tiles_per_launch = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
+            # DRAM bytes per 128 x 128 x 128 tile-update of C, from an ncu capture of two large launches
+            # of the rank-128 update (141.1 MB for 1485 tiles); a launch with a longer reduction touches
+            # its C tile once for all of it, so the figure is scaled by output tiles, not by flop
+            tile_updates = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
             roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
                         "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
-                        "traffic": 95.0e3 * tiles_per_launch if top == "umma_gemm" else None,
-                        "traffic_note": "bytes per average launch, scaled by tiles from an ncu capture of two large launches",
+                        "traffic": 95.0e3 * tile_updates if top == "umma_gemm" else None,
+                        "traffic_source": "scaled from an ncu capture (95 KB of DRAM traffic per 128x128 tile of a rank-128 "
+                                          "update), not measured in this run",
                         "fp32_equivalent_tflops": v["work"] / secs / 1e12,
                         "padded_tflops": v["work2"] / secs / 1e12,
                         "note": "algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products "
-                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once",
-                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / min(steps, 4),
+                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once; "
+                                "timed on one stream with full grids",
+                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / n_prof,
                         "peak_source": peaks["source"] + " (sustained bf16)"}
         else:
             achieved = v["work"] / (v["ms"] / 1e3) / 1e9
@@ -324,7 +423,7 @@ def run_b200(args):
 
     # ---- gate_proj + up_proj of an expert share their input, hence their Hessian: quantized as a
     # tied pair they share one factorisation (quant.py --tie_gptq_handles; the reference factors twice)
-    from moe_quant_b200 import quantize_tied
+    weights, hessians, n_experts = cx.weights, cx.hessians, cx.n_experts
     n_pairs = max(2, steps_aux // 4)
     pair_pool = [torch.cuda.Stream(device=dev) for _ in range(min(n_streams, n_pairs))]
 
@@ -334,9 +433,8 @@ def run_b200(args):
             gate = make_handles(1)[0]
             gate.layer.weight = nn.Parameter(weights[i % n_experts], requires_grad=False)
             gate.H = hessians[i % n_experts].clone()
-            up_layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
-            up_layer.weight = nn.Parameter(weights[(i + 1) % n_experts], requires_grad=False)
-            out.append((gate, GPTQ(up_layer, GROUP, True, 1e-2, 128, tied_gptq_handle=gate)))
+            up = GPTQ(_linear(weights[(i + 1) % n_experts]), GROUP, True, 1e-2, 128, tied_gptq_handle=gate)
+            out.append((gate, up))
         return out
 
     def run_pairs(pairs):
@@ -356,51 +454,59 @@ def run_b200(args):
     del pre_pairs
     pairs = make_pairs(n_pairs)
     barrier()
-    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0, p1 = _event_pair()
     p0.record()
     pair_results = run_pairs(pairs)
     p1.record()
     barrier()
     tied_layers_per_s = 2 * n_pairs / (p0.elapsed_time(p1) / 1e3)
     del pairs, pair_results
-    # ---- Hessian accumulation rate (the second half of the headline metric)
-    g = torch.Generator(device=dev).manual_seed(seed)
-    X = (torch.randn(TOKENS, C, generator=g, device=dev)).to(torch.bfloat16)
-    Hs = torch.zeros(C, C, dtype=torch.float32, device=dev)
-    for _ in range(3):
-        ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(10):
-        ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
-    e1.record()
-    torch.cuda.synchronize()
-    h_ms = e0.elapsed_time(e1) / 10
-    del Hs
 
-    # ---- end to end through the handle with host buffers
+    # ---- Hessian accumulation rate (the second half of the headline metric), 16-bit and fp32 activations
+    hess = {}
+    for name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        X = _randn_acts(TOKENS, C, dt, cx.seed, dev)
+        Hs = torch.zeros(C, C, dtype=torch.float32, device=dev)
+        for _ in range(3):
+            ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
+        torch.cuda.synchronize()
+        e0, e1 = _event_pair()
+        n_rep = 10
+        e0.record()
+        for _ in range(n_rep):
+            ops.hessian_accum(Hs, X, 0.5, 1.0 / TOKENS)
+        e1.record()
+        torch.cuda.synchronize()
+        h_ms = e0.elapsed_time(e1) / n_rep
+        hess[name] = {"ms": h_ms, "tflops_2NC2": 2.0 * TOKENS * C * C / h_ms / 1e9,
+                      "tflops_unique": TOKENS * C * (C + 1) / h_ms / 1e9, "tokens": TOKENS,
+                      "products_per_fp32_product": 1 if dt != torch.float32 else 6}
+        del Hs, X
+
+    # ---- end to end through the handles with host buffers.  A step is one layer; layers come in
+    # gate_proj/up_proj pairs of one expert, which see the same activations: X is uploaded once per
+    # expert, the Hessian accumulated once, both layers quantized with one factorisation.
     Wh = [w.cpu().pin_memory() for w in weights]
-    Xh = synthetic.activations(TOKENS, C, seed, torch.bfloat16).pin_memory()
-    # one set of pinned result buffers per stream: steps on different streams overlap
+    Xh = synthetic.activations(TOKENS, C, cx.seed, torch.bfloat16).pin_memory()
     pool = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
-    q_host = [torch.empty(R, C, dtype=torch.uint8).pin_memory() for _ in pool]
-    s_host = [torch.empty(R, C // GROUP, dtype=torch.bfloat16).pin_memory() for _ in pool]
-    h2d = Wh[0].numel() * 2 + Xh.numel() * 2
-    d2h = q_host[0].numel() + s_host[0].numel() * 2
+    q_host = [[torch.empty(R, C, dtype=torch.uint8).pin_memory() for _ in range(2)] for _ in pool]
+    s_host = [[torch.empty(R, C // GROUP, dtype=torch.bfloat16).pin_memory() for _ in range(2)] for _ in pool]
+    h2d_pair = 2 * Wh[0].numel() * 2 + Xh.numel() * 2
+    d2h_pair = 2 * (q_host[0][0].numel() + s_host[0][0].numel() * 2)
 
-    def e2e_step(i):
+    def e2e_pair(i):
         k = i % n_streams
-        W = Wh[i % n_experts].to(dev, non_blocking=True)
+        Wg = Wh[i % n_experts].to(dev, non_blocking=True)
+        Wu = Wh[(i + 1) % n_experts].to(dev, non_blocking=True)
         Xd = Xh.to(dev, non_blocking=True)
-        layer = nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device="meta")
-        layer.weight = nn.Parameter(W, requires_grad=False)
-        h = GPTQ(layer, GROUP, True, 1e-2, 128)
-        h.update(Xd)
-        q, s, _z = h.quantize(BITS)
-        q_host[k].copy_(q, non_blocking=True)
-        s_host[k].copy_(s, non_blocking=True)
-        h.reset()
+        gate = GPTQ(_linear(Wg), GROUP, True, 1e-2, 128)
+        up = GPTQ(_linear(Wu), GROUP, True, 1e-2, 128, tied_gptq_handle=gate)
+        gate.update(Xd)
+        for j, (q, s, _z) in enumerate(quantize_tied([gate, up], BITS)):
+            q_host[k][j].copy_(q, non_blocking=True)
+            s_host[k][j].copy_(s, non_blocking=True)
+        gate.reset()
+        up.reset()
 
     def e2e_run(n):
         cur = torch.cuda.current_stream(dev)
@@ -408,52 +514,278 @@ def run_b200(args):
             st.wait_stream(cur)
         for i in range(n):
             with torch.cuda.stream(pool[i % n_streams]):
-                e2e_step(i)
+                e2e_pair(i)
         for st in pool:
             cur.wait_stream(st)
 
-    e2e_steps = steps_aux
-    e2e_run(max(e2e_steps, n_streams))
+    e2e_pairs = max(n_streams, steps_aux // 2)
+    e2e_run(e2e_pairs)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_run(e2e_steps)
-    e1.record()
+    e2e_ms = []
+    for _ in range(min(cx.reps, 3)):
+        e0, e1 = _event_pair()
+        e0.record()
+        e2e_run(e2e_pairs)
+        e1.record()
+        barrier()
+        e2e_ms.append(cx.max_over_ranks(e0.elapsed_time(e1)))
+    e2e_value = world * 2 * e2e_pairs / (statistics.median(e2e_ms) / 1e3)
+    # the host link by itself, every rank copying at once: the ceiling of any end-to-end rate
+    big = torch.empty(512 << 20, dtype=torch.uint8).pin_memory()
+    dst = torch.empty_like(big, device=dev)
+    dst.copy_(big, non_blocking=True)
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * e2e_steps / (float(t.item()) / 1e3)
+    c0, c1 = _event_pair()
+    c0.record()
+    for _ in range(4):
+        dst.copy_(big, non_blocking=True)
+    c1.record()
+    barrier()
+    h2d_gbs = 4 * big.numel() / (cx.max_over_ranks(c0.elapsed_time(c1)) / 1e3) / 1e9
+    del big, dst
 
+    parity = _guarded(parity_sample, cx) if rank == 0 else None
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not cx_no_cpu(cx):
         cores = os.cpu_count() or 1
         v, ms, _ = cpu_layers_per_s(2, 1, cores)
         cpu = {"value": v, "unit": "layers/s", "cores": cores, "kind": "port",
                "sample": f"2 full 2048x7168 layers after 1 warm-up ({ms:.0f} ms each), torch CPU oracle, {cores} threads"}
 
+    config = dict(CONFIG)
+    config.update({"experts_rotated": n_experts, "tokens_per_expert": cx.tokens,
+                   "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
+                   "parallelism": f"ep{world}", "streams": n_streams, "timed_passes": cx.reps,
+                   "untimed_pass_before": "one full pass of K steps (allocator and workspaces warm), then W >= 3 honoured",
+                   "single_stream_layers_per_s_per_gpu": steps_aux / (ms_single / 1e3),
+                   "tied_gate_up_layers_per_s_per_gpu": tied_layers_per_s,
+                   "e2e_step": "one layer of a gate_proj/up_proj pair: X uploaded once per expert, one factorisation per pair",
+                   "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"})
+    return {
+        "metric": METRIC, "value": value, "unit": "layers/s", "n_gpus": world, "steps": steps, "warmup": cx.warmup,
+        "ms_per_step": ms_med / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config,
+        "passes_ms": [round(p, 3) for p in passes],
+        "spread": (max(passes) - min(passes)) / ms_med,
+        "roofline": roofline, "kernel_time_shares": shares, "kernel_us_per_layer_one_stream": per_layer_us,
+        "parity": parity, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "layers/s", "h2d_bytes_per_step": h2d_pair // 2, "d2h_bytes_per_step": d2h_pair // 2,
+                "h2d_gbs_per_rank_in_run": e2e_value / world * (h2d_pair / 2) / 1e9,
+                "h2d_gbs_per_rank_link_alone": h2d_gbs, "passes_ms": [round(p, 3) for p in e2e_ms]},
+        "gpu_launches": int(launches),
+        "clocks": cx.clocks.result,
+        "hessian_accum": hess,
+        "hessian_issues": int(issues), "engine_fault": int(fault),
+    }
+
+
+def cx_no_cpu(cx):
+    return getattr(cx, "no_cpu_baseline", False)
+
+
+def parity_sample(cx):
+    """Untimed: one of the benchmark's own experts (its ragged token count) quantized once, the
+    first 64 rows compared with the CPU oracle fed with the same Hessian."""
+    from moe_quant_b200 import GPTQ
+    from oracle import gptq_oracle as O
+
+    rows = 64
+    h = cx.make_handles(1)[0]
+    H_raw = h.H.clone()
+    q, s, z = h.quantize(BITS)
+    Wc = cx.weights[0][:rows].cpu()
+    want = O.quantize_layer(Wc, H_raw.cpu(), bits=BITS, group_size=GROUP, rel_damp=1e-2, block_size=128)
+    got = O.dequantize_linear_weight(q[:rows].cpu(), s[:rows].cpu(), z[:rows].cpu()).float()
+    ref = O.dequantize_linear_weight(want["qweight"], want["scale"], want["zero"]).float()
+    Hc = cx.hessians[0].cpu()
+    return {"rows": rows, "tokens": cx.tokens[0], "code_agreement": O.code_agreement(q[:rows].cpu(), want["qweight"]),
+            "scales_equal": bool(torch.equal(s[:rows].cpu().float(), want["scale"].float())),
+            "recon_error": O.reconstruction_error(Wc.float(), got, Hc),
+            "recon_error_oracle": O.reconstruction_error(Wc.float(), ref, Hc)}
+
+
+# ---------------------------------------------------------------------------- the other named workloads
+def _time_layers(cx, build, n, streams):
+    """layers/s of `n` independent handles made by build(i), spread over `streams` CUDA streams."""
+    from moe_quant_b200 import quantize_many
+    warm = quantize_many([build(i) for i in range(n)], BITS, streams=streams)
+    torch.cuda.synchronize()
+    del warm
+    ms = []
+    for _ in range(3):
+        hs = [build(i) for i in range(n)]
+        torch.cuda.synchronize()
+        e0, e1 = _event_pair()
+        e0.record()
+        res = quantize_many(hs, BITS, streams=streams)
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+        del hs, res
+    return n / (statistics.median(ms) / 1e3), statistics.median(ms)
+
+
+def wl_down_proj(cx):
+    """Expert down_proj, 7168 x 2048 fp16, 8192 calibration tokens, group size 32 / 64 / 128 /
+    per-channel, followed by the int4 -> int32 packing of the codes."""
+    from moe_quant_b200 import GPTQ, ops
+    dev = cx.dev
+    rows, cols, toks = 7168, 2048, 8192
+    W = _randn_weight(rows, cols, torch.float16, 77, dev)
+    X = _randn_acts(toks, cols, torch.float16, 78, dev)
+    H = torch.zeros(cols, cols, dtype=torch.float32, device=dev)
+    ops.hessian_accum(H, X, 0.0, 2.0 / toks)
+    out = {"shape": [rows, cols], "dtype": "fp16", "tokens": toks, "groups": {}}
+    for g in (32, 64, 128, cols):
+        def build(i, g=g):
+            h = GPTQ(_linear(W), g, True, 1e-2, 128)
+            h.H = H.clone()
+            h.num_samples = toks
+            return h
+        many, _ = _time_layers(cx, build, 16, cx.n_streams)
+        one, ms1 = _time_layers(cx, build, 4, 1)
+        out["groups"][str(g)] = {"layers_per_s": many, "layers_per_s_one_stream": one,
+                                 "fp32_equiv_tflops_one_stream": layer_flop(rows, cols) / (ms1 / 4 / 1e3) / 1e12}
+    # packing alone: 16 different code matrices (235 MB, larger than L2), one launch each
+    codes = [torch.randint(0, 16, (rows, cols), dtype=torch.uint8, device=dev) for _ in range(16)]
+    for c in codes:
+        ops.pack_int4(c)
+    torch.cuda.synchronize()
+    e0, e1 = _event_pair()
+    e0.record()
+    for _ in range(4):
+        for c in codes:
+            ops.pack_int4(c)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 64
+    gbs = 1.5 * rows * cols / (us * 1e-6) / 1e9
+    out["pack"] = {"us_per_launch": us, "gbs": gbs, "bytes_per_launch": 1.5 * rows * cols,
+                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": cx.peaks["hbm"], "unit": "GB/s",
+                                "frac": gbs / cx.peaks["hbm"], "peak_source": cx.peaks["source"]}}
+    return out
+
+
+def wl_moe_layer(cx):
+    """One rank's shard of a whole MoE layer: 32 routed experts x {gate_proj, up_proj (tied to gate),
+    down_proj}, ragged token counts (top-8 routing of 32 x 4096 tokens over 256 experts), Hessian
+    accumulation included.  No collective: routed experts are expert-parallel."""
+    from moe_quant_b200 import GPTQ, ops, quantize_many, quantize_tied, synthetic
+    dev, rank = cx.dev, cx.rank
+    n_exp, hidden, inter = 32, 7168, 2048
+    counts = synthetic.ragged_expert_counts(32 * 4096, 256, 8, 99)
+    mine = [int(counts[(rank * n_exp + e) % 256]) for e in range(n_exp)]
+    Wg = [_randn_weight(inter, hidden, torch.bfloat16, 1000 + e, dev) for e in range(n_exp)]
+    Wu = [_randn_weight(inter, hidden, torch.bfloat16, 2000 + e, dev) for e in range(n_exp)]
+    Wd = [_randn_weight(hidden, inter, torch.bfloat16, 3000 + e, dev) for e in range(n_exp)]
+    Xs = [_randn_acts(m, hidden, torch.bfloat16, 4000 + e, dev) for e, m in enumerate(mine)]
+    Xd = [_randn_acts(m, inter, torch.bfloat16, 5000 + e, dev) for e, m in enumerate(mine)]
+    pool = [torch.cuda.Stream(device=dev) for _ in range(cx.n_streams)]
+
+    def one_pass():
+        gates = [GPTQ(_linear(w), GROUP, True, 1e-2, 128) for w in Wg]
+        ups = [GPTQ(_linear(w), GROUP, True, 1e-2, 128, tied_gptq_handle=g) for w, g in zip(Wu, gates)]
+        downs = [GPTQ(_linear(w), GROUP, True, 1e-2, 128) for w in Wd]
+        cx.barrier()
+        e0, e1, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for e in range(n_exp):                       # the Hessian pass: what the forward hooks do
+            gates[e].update(Xs[e])
+            downs[e].update(Xd[e])
+        e1.record()
+        cur = torch.cuda.current_stream(dev)
+        for st in pool:
+            st.wait_stream(cur)
+        res = []
+        for e in range(n_exp):
+            with torch.cuda.stream(pool[e % len(pool)]):
+                res.append(quantize_tied([gates[e], ups[e]], BITS))
+        for st in pool:
+            cur.wait_stream(st)
+        res.append(quantize_many(downs, BITS, streams=cx.n_streams))
+        e2.record()
+        cx.barrier()
+        issues = sum(h.has_hessian_issues() for h in gates + ups + downs)
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), issues
+
+    one_pass()
+    runs = [one_pass() for _ in range(2)]
+    h_ms = statistics.median(r[0] for r in runs)
+    q_ms = statistics.median(r[1] for r in runs)
+    total = cx.max_over_ranks(h_ms + q_ms)
+    flop_h = sum(m * hidden * (hidden + 1) + m * inter * (inter + 1) for m in mine)
+    return {"experts_per_rank": n_exp, "layers_per_rank": 3 * n_exp, "tokens_per_expert_min_mean_max":
+            [min(mine), sum(mine) / n_exp, max(mine)], "hessian_pass_ms": h_ms, "quantize_ms": q_ms,
+            "layer_ms_max_over_ranks": total, "layers_per_s_all_ranks": cx.world * 3 * n_exp / (total / 1e3),
+            "hessian_tflops_unique": flop_h / (h_ms / 1e3) / 1e12, "hessian_issues": int(runs[-1][2])}
+
+
+def wl_mla(cx):
+    """The five MLA projections of a block (shared layers: every rank holds a slice of the
+    calibration tokens).  Per rank: Hessian accumulation from its tokens; then
+    gptq.quantize_shared: Hessians reduced to owner ranks, owners quantize side by side, results
+    broadcast.  With one GPU the five layers run on five streams."""
+    from moe_quant_b200 import GPTQ
+    from moe_quant_b200.gptq import quantize_shared, shared_layer_owners
+    dev, rank, world = cx.dev, cx.rank, cx.world
+    shapes = [("q_a_proj", 1536, 7168), ("q_b_proj", 24576, 1536), ("kv_a_proj_with_mqa", 576, 7168),
+              ("kv_b_proj", 32768, 512), ("o_proj", 7168, 16384)]
+    toks = 8192                                     # per rank
+    Ws = [_randn_weight(r, c, torch.bfloat16, 600 + i, dev) for i, (_, r, c) in enumerate(shapes)]
+    Xs = {c: _randn_acts(toks, c, torch.bfloat16, 700 + c + rank, dev) for c in sorted({c for _, _, c in shapes})}
+
+    def handles():
+        return [GPTQ(_linear(w), GROUP, True, 1e-2, 128, is_distributed=True) for w in Ws]
+
+    def one_pass(shared: bool):
+        hs = handles()
+        cx.barrier()
+        e0, e1, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for h, (_, _, c) in zip(hs, shapes):
+            h.update(Xs[c])
+        e1.record()
+        if shared:
+            res = quantize_shared(hs, BITS, streams=5)
+        else:
+            res = [h.quantize(BITS) for h in hs]    # the reference's scheme: all-reduce, rank 0 works, broadcast
+        e2.record()
+        cx.barrier()
+        bad = sum(h.has_hessian_issues() for h in hs)
+        del res
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), bad
+
+    one_pass(True)
+    a = [one_pass(True) for _ in range(2)]
+    one_pass(False)
+    b = [one_pass(False) for _ in range(2)]
+    own_ms = cx.max_over_ranks(statistics.median(r[1] for r in a))
+    ref_ms = cx.max_over_ranks(statistics.median(r[1] for r in b))
+    h_ms = cx.max_over_ranks(statistics.median(r[0] for r in a))
+    # each projection alone on one stream (rank 0's GPU, no collective): the terms of the sum
+    alone = {}
     if rank == 0:
-        line = {
-            "metric": METRIC, "value": value, "unit": "layers/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "experts_rotated": n_experts, "tokens_per_expert": tokens,
-                       "l2": "inputs larger than L2: each step touches a different expert's 29 MB weight and 205 MB Hessian",
-                       "parallelism": f"ep{world}", "streams": n_streams,
-                       "single_stream_layers_per_s_per_gpu": steps_aux / (ms_single / 1e3),
-                       "tied_gate_up_layers_per_s_per_gpu": tied_layers_per_s, "math": "tcgen05 split-bf16 x3 planes (6 products), fp32 TMEM accumulation"},
-            "roofline": roofline, "kernel_time_shares": shares,
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "layers/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches),
-            "clocks": clocks.result,
-            "hessian_accum": {"ms": h_ms, "tflops_2NC2": 2.0 * TOKENS * C * C / h_ms / 1e9,
-                              "tflops_unique": TOKENS * C * (C + 1) / h_ms / 1e9, "tokens": TOKENS, "dtype": "bf16"},
-            "hessian_issues": int(issues), "engine_fault": int(fault),
-        }
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        for (name, r, c), w in zip(shapes, Ws):
+            ms = []
+            for _ in range(3):
+                h = GPTQ(_linear(w), GROUP, True, 1e-2, 128)
+                h.update(Xs[c])
+                torch.cuda.synchronize()
+                e0, e1 = _event_pair()
+                e0.record()
+                h.quantize(BITS)
+                e1.record()
+                torch.cuda.synchronize()
+                ms.append(e0.elapsed_time(e1))
+            t = statistics.median(ms[1:])
+            alone[name] = {"ms": t, "fp32_equiv_tflops": layer_flop(r, c) / (t / 1e3) / 1e12}
+    cx.barrier()
+    flop_h = sum(toks * c * (c + 1) for _, _, c in shapes)
+    return {"tokens_per_rank": toks, "owners": shared_layer_owners(handles(), world),
+            "hessian_pass_ms": h_ms, "hessian_tflops_unique_per_rank": flop_h / (h_ms / 1e3) / 1e12,
+            "quantize_ms_owner_ranks": own_ms, "quantize_ms_rank0_scheme": ref_ms,
+            "each_alone_one_stream": alone, "sum_alone_ms": sum(v["ms"] for v in alone.values()) if alone else None,
+            "hessian_issues": int(a[-1][2])}
 
 
 def run_single_layer(args):
@@ -462,10 +794,8 @@ def run_single_layer(args):
     from moe_quant_b200 import _lib, ops
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    g = torch.Generator(device="cuda").manual_seed(0)
-    W = (0.02 * torch.randn(R, C, generator=g, device=dev)).to(torch.bfloat16)
-    chan = torch.exp(torch.randn(C, generator=g, device=dev))
-    X = (torch.randn(TOKENS, C, generator=g, device=dev) * chan).to(torch.bfloat16)
+    W = _randn_weight(R, C, torch.bfloat16, 0, dev)
+    X = _randn_acts(TOKENS, C, torch.bfloat16, 1, dev)
     H = torch.zeros(C, C, device=dev)
     ops.hessian_accum(H, X, 0.0, 2.0 / TOKENS)
     for _ in range(max(1, args.steps)):
@@ -480,8 +810,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--reps", type=int, default=5, help="how many times the pass of K steps is timed (median reported)")
     ap.add_argument("--streams", type=int, default=8, help="CUDA streams the independent layers are spread over")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="all", choices=["all", "headline", "down_proj", "mla", "moe_layer"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-layer", action="store_true",
                     help="run one Hessian accumulation and --steps layers untimed (profiler captures)")

@@ -430,31 +430,33 @@ def quantize_shared(handles: Sequence[GPTQ], bits: int, streams: int = 4, want_e
     """
     handles = list(handles)
     bits = int(bits)
-    if not (dist_utils.is_dist_available_and_initialized() and dist_utils.get_world_size() > 1):
-        out = [h.quantize(bits) for h in handles]
-        return (out, [_relative_error(h, r) for h, r in zip(handles, out)]) if want_error else out
-    world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
+    if not handles:
+        return ([], []) if want_error else []
+    distributed = dist_utils.is_dist_available_and_initialized() and dist_utils.get_world_size() > 1
+    world, rank = (dist_utils.get_world_size(), dist_utils.get_rank()) if distributed else (1, 0)
     owners = shared_layer_owners(handles, world)
     device = handles[0].W_device
     roots = [i for i, h in enumerate(handles) if h.tied_gptq_handle is None]
 
     # ---- Hessians to their owners, weighted by token counts (ranks may hold different numbers)
-    counts = torch.tensor([float(handles[i].num_samples if handles[i].H is not None else 0) for i in roots],
-                          dtype=torch.float64, device=device)
-    totals = counts.clone()
-    dist.all_reduce(totals, op=dist.ReduceOp.SUM)
-    for k, i in enumerate(roots):
-        h = handles[i]
-        total = float(totals[k].item())
-        if total == 0.0:                       # nobody saw a token: identity Hessian (src/gptq.py:129-136)
-            h.H = None
-            continue
-        if h.H is None:
-            h.H = torch.zeros(h.d_col, h.d_col, device=device, dtype=torch.float32)
-        else:
-            h.H.mul_(h.num_samples / total)
-        dist.reduce(h.H, dst=owners[i], op=dist.ReduceOp.SUM)
-        h.num_samples = int(total)
+    if distributed:
+        counts = torch.tensor([float(handles[i].num_samples if handles[i].H is not None else 0) for i in roots],
+                              dtype=torch.float64, device=device)
+        totals = counts.clone()
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+        totals = totals.tolist()
+        for k, i in enumerate(roots):
+            h = handles[i]
+            total = float(totals[k])
+            if total == 0.0:                       # nobody saw a token: identity Hessian (src/gptq.py:129-136)
+                h.H = None
+                continue
+            if h.H is None:
+                h.H = torch.zeros(h.d_col, h.d_col, device=device, dtype=torch.float32)
+            else:
+                h.H.mul_(h.num_samples / total)
+            dist.reduce(h.H, dst=owners[i], op=dist.ReduceOp.SUM)
+            h.num_samples = int(total)
     for h in handles:
         was_distributed, h.is_distributed = h.is_distributed, False     # the collectives are done here
         try:
@@ -509,7 +511,8 @@ def quantize_shared(handles: Sequence[GPTQ], bits: int, streams: int = 4, want_e
         if want_error:
             e = _relative_error(h, results[i])
             status[i, 3] = float("nan") if e is None else e
-    dist.all_reduce(status, op=dist.ReduceOp.SUM)          # every row has exactly one writer
+    if distributed:
+        dist.all_reduce(status, op=dist.ReduceOp.SUM)      # every row has exactly one writer
     status = status.cpu()
     pending = []
     for i, h in enumerate(handles):
@@ -522,8 +525,9 @@ def quantize_shared(handles: Sequence[GPTQ], bits: int, streams: int = 4, want_e
             results[i] = (torch.empty(h.d_row, h.d_col, device=device, dtype=torch.uint8),
                           torch.empty(h.d_row, h.d_col // g, device=device, dtype=h.W_dtype),
                           torch.empty(h.d_row, h.d_col // g, device=device, dtype=h.W_dtype))
-        for t in results[i]:
-            pending.append(dist.broadcast(t, src=owners[i], async_op=True))
+        if distributed:
+            for t in results[i]:
+                pending.append(dist.broadcast(t, src=owners[i], async_op=True))
     for work in pending:
         work.wait()
     return (results, errors) if want_error else results

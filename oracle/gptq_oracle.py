@@ -15,10 +15,14 @@ Parity status
   are PINNED: the golden fixtures under ``tests/golden`` were produced by the
   reference's own code imported unchanged (``tests/golden/make_golden.py``).
 * The column sweep (``src/gptq_loop.py:141-148``) is Triton-only in the
-  reference, cannot execute without a GPU, and the reference ships no golden
-  vectors or tests.  The sweep restated here follows the Triton kernel text
-  line by line, but it is "parity unpinned": no output of the reference's own
-  sweep exists to check it against.
+  reference and cannot execute without a GPU.  It is PINNED by
+  ``tests/golden/sweep_triton.npz``: codes produced on a B200 by the reference's
+  own ``gptq_loop`` (Triton kernels + ``addmm_``) and by its whole ``GPTQ`` handle,
+  imported unchanged (``tests/golden/make_golden_sweep_gpu.py``).  The sweep
+  restated here reproduces them (``tests/test_triton_pin.py``).  The codes inside
+  the CPU fixtures of ``make_golden.py`` come from this restatement patched into
+  the reference's pipeline; the device run showed them identical to the Triton
+  loop's on every fixture.
 * ``compressed_tensors.pack_to_int32`` (third-party, unpinned by the reference;
   0.15.0.1 here) is restated in :func:`pack_to_int32`; the fixtures hold the
   installed library's words.

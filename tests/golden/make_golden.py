@@ -11,7 +11,9 @@ sweep (``src/gptq_loop.py``); ``src.gptq_loop.gptq_loop`` is therefore replaced
 by the restatement in ``oracle/gptq_oracle.py`` for the duration of the run.
 Everything else in the fixtures (Hessians, damped Hessians, the row-normalised
 factor, scales, zeros, the transposes and casts at the end of ``_quantize``,
-the packed words) is the reference's own arithmetic.
+the packed words) is the reference's own arithmetic.  The sweep itself is pinned
+separately by ``make_golden_sweep_gpu.py``, which runs the reference's Triton loop
+on a GPU over these same fixtures (``sweep_triton.npz``).
 
 The fixtures store inputs as well as outputs, so no random-number generator
 has to agree between the machine that wrote them and the one that reads them.

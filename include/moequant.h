@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define MQ_ABI_VERSION 1
+#define MQ_ABI_VERSION 2
 
 typedef enum {
   MQ_OK = 0,
@@ -155,6 +155,16 @@ int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag_out, int m
 int mq_absmax_scales(const float* W, int64_t R, int64_t C, int64_t ldw, int64_t group,
                      int bits, int out_dtype, float* scale, void* stream);
 
+/* MSE refinement of the symmetric grid (QuantizationScale.MSE, src/quant_utils.py:104-192, 218-230):
+ * every scale[r, j] (as written by mq_absmax_scales, rounded through out_dtype) is replaced by
+ * round_to(out_dtype, scale * shrink[i*]) where i* minimises
+ *   sum_c | dequant(quant(W[r, c]; round_to(out_dtype, scale * shrink[i]))) - W[r, c] |^norm
+ * over the group.  shrink: n_shrink fp32 factors on the device (the reference uses
+ * linspace(1, 0.2, 100)); norm 2.4 in the reference.  */
+int mq_mse_scales(const float* W, int64_t R, int64_t C, int64_t ldw, int64_t group, int bits,
+                  int out_dtype, const float* shrink, int n_shrink, float norm, float* scale,
+                  void* stream);
+
 /* ------------------------------------------------------------------ a6 + a7 + a8
  * GPTQ column sweep over W (R,C) fp32 (destroyed), given Uhat (C,C) upper/unit.
  * Replaces gptq_loop / quantize_error_triton_kernel / addvv_triton_kernel / the lazy
@@ -162,6 +172,9 @@ int mq_absmax_scales(const float* W, int64_t R, int64_t C, int64_t ldw, int64_t 
  *   scale, zero : element (r, c) is  base[r*row_stride + (c/group)*group_stride];
  *                 zero may be NULL (then (maxq+1)/2 is used).
  *   codes       : (R,C) uint8 out, row-major, values 0..maxq.
+ *   packed      : optional (R, C/8) int32 out: the same codes in the compressed-tensors layout of
+ *                 mq_pack_int4 (pack_quantized_model.py:57-75), written by the sweep itself so
+ *                 that no packing pass reads the codes back.  Needs bits == 4 and zero == NULL.
  *   dequantized : optional (R,C) out of out_dtype holding round_to(out_dtype,(q-zero)*scale).
  *   out_dtype   : the layer dtype that dequantized values are rounded through inside the
  *                 sweep (src/quant_utils.py:37-49).
@@ -175,7 +188,7 @@ int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw,
                   const float* scale, const float* zero, int64_t group,
                   int64_t row_stride, int64_t group_stride,
                   int bits, int out_dtype,
-                  uint8_t* codes, void* dequantized, const float* W_original, int64_t ldwo,
+                  uint8_t* codes, int32_t* packed, void* dequantized, const float* W_original, int64_t ldwo,
                   int math, int split, void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
 
@@ -185,14 +198,16 @@ size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
  * it ends up damped like the reference's handle.H), scales, Uhat, sweep.
  *   Wsrc (R,C) of w_dtype is not modified.
  *   scale_out (R, C/group) fp32 values already rounded through w_dtype.
- *   n_tied > 1: Wsrc/codes/scale_out/dequantized are arrays of n_tied device pointers
+ *   packed (optional, NULL or n_tied pointers): (R, C/8) int32 words per layer, see mq_gptq_sweep.
+ *   n_tied > 1: Wsrc/codes/packed/scale_out/dequantized are arrays of n_tied device pointers
  *   passed from HOST memory; the layers share H (tied gate_proj/up_proj handles,
  *   quant.py:258-262) and therefore one factorisation.  With n_tied == 1 the same
  *   arguments are still pointer arrays of length 1.
  * workspace: mq_quantize_layer_workspace_bytes(...).  */
 int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tied, int64_t R, int64_t C,
                       float* H, int64_t ldh, int64_t group, int bits, float rel_damp,
-                      uint8_t* const* codes, float* const* scale_out, void* const* dequantized,
+                      uint8_t* const* codes, int32_t* const* packed, float* const* scale_out,
+                      void* const* dequantized,
                       mq_layer_flags* flags, int math, int split_hinv, int split_sweep,
                       void* workspace, size_t workspace_bytes, void* stream);
 size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64_t C, int math,

@@ -45,14 +45,16 @@ SIGNATURES = {
                               c_void_p, c_size_t, c_void_p]),
     "mq_hinv_upper_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "mq_absmax_scales": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "mq_mse_scales": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_float,
+                              c_void_p, c_void_p]),
     "mq_gptq_sweep": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
-                              c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                              c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                               c_void_p, c_size_t, c_void_p]),
     "mq_chol_unit_factor": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t,
                                     c_void_p]),
     "mq_gptq_sweep_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
     "mq_quantize_layer": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
-                                  c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                  c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                   c_size_t, c_void_p]),
     "mq_quantize_layer_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int, c_int, c_int]),
     "mq_dequantize": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,

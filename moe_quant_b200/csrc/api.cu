@@ -26,7 +26,7 @@ size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
                void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st,
-               const float* col_div);
+               const float* col_div, int32_t* packed);
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
                      Workspace& ws, cudaStream_t st, bool upper_only, bool unscaled);
 int hessian_accum_tensor(const void* X, int x_dtype, int64_t m, int64_t C, int64_t ldx, float* H, int64_t ldh, float beta,
@@ -127,7 +127,7 @@ extern "C" size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64
 
 extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tied, int64_t R, int64_t C, float* H,
                                  int64_t ldh, int64_t group, int bits, float rel_damp, uint8_t* const* codes,
-                                 float* const* scale_out, void* const* dequantized, mq_layer_flags* flags, int math,
+                                 int32_t* const* packed, float* const* scale_out, void* const* dequantized, mq_layer_flags* flags, int math,
                                  int split_hinv, int split_sweep, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace mq;
   MQ_REQUIRE(Wsrc && codes && scale_out && H && flags, MQ_ERR_ARGUMENT, "mq_quantize_layer: null pointer");
@@ -143,6 +143,8 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   for (int i = 0; i < n_tied; ++i) {
     MQ_REQUIRE(Wsrc[i] && codes[i] && scale_out[i], MQ_ERR_ARGUMENT, "mq_quantize_layer: null pointer for tied layer %d", i);
     MQ_REQUIRE(aligned(codes[i], 4), MQ_ERR_ALIGNMENT, "mq_quantize_layer: codes must be 4-byte aligned");
+    MQ_REQUIRE(!packed || (packed[i] && bits == 4 && aligned(packed[i], 4)), MQ_ERR_UNSUPPORTED,
+               "mq_quantize_layer: packed words need bits == 4 and a 4-byte aligned buffer per layer");
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace ws(workspace, workspace_bytes);
@@ -186,7 +188,8 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
     MQ_CUDA(cudaMemcpyAsync(Wo[i], Wf[i], (size_t)R * C * sizeof(float), cudaMemcpyDeviceToDevice, st));
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
     MQ_TRY(gptq_sweep(Wf[i], R, C, C, U, C, scale_out[i], nullptr, group, C / group, 1, bits, w_dtype, codes[i],
-                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st, unscaled ? diag : nullptr));
+                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st, unscaled ? diag : nullptr,
+                      packed ? packed[i] : nullptr));
   }
   return MQ_OK;
 }

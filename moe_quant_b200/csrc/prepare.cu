@@ -158,6 +158,45 @@ __global__ void __launch_bounds__(256) absmax_scales_kernel(const float* __restr
   }
 }
 
+// ---------------------------------------------------------------- MSE scale search
+// One warp per (row, group): the absmax scale s0 is shrunk by each candidate factor p_i,
+//   s_i = round_to_dtype(s0 * p_i),  loss_i = sum_c |dequant(quant(x_c; s_i)) - x_c|^norm,
+// and replaced by s0 * p_argmin rounded through the dtype (mse_scale_triton_kernel,
+// src/quant_utils.py:104-139).  |d|^norm is exp(norm * log|d|) as in tl_pow (src/quant_utils.py:25-27),
+// which is 0 for d == 0.  Of equal losses the first candidate wins; candidates with equal losses
+// almost always have equal rounded scales, so the choice among them does not change the result.
+template <int DT>
+__global__ void __launch_bounds__(256) mse_scales_kernel(const float* __restrict__ W, int64_t R, int64_t C, int64_t ldw,
+                                                         int64_t group, float maxq, float zero,
+                                                         const float* __restrict__ p, int p_size, float norm,
+                                                         float* __restrict__ scale) {
+  const int64_t G = C / group;
+  const int64_t n_seg = R * G;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t seg = warp; seg < n_seg; seg += n_warps) {
+    const int64_t r = seg / G, gi = seg - r * G;
+    const float* x = W + r * ldw + gi * group;
+    const float s0 = scale[seg];
+    float best = 0.0f;
+    int best_i = -1;
+    for (int i = 0; i < p_size; ++i) {
+      const float s = round_through<DT>(__fmul_rn(s0, __ldg(p + i)));
+      float loss = 0.0f;
+      for (int64_t k = lane; k < group; k += 32) {
+        const float xv = __ldg(x + k);
+        const float q = fminf(fmaxf(floorf(__fadd_rn(__fadd_rn(__fdiv_rn(xv, s), zero), 0.5f)), 0.0f), maxq);
+        const float y = round_through<DT>(__fmul_rn(q - zero, s));
+        loss += __expf(__logf(fabsf(y - xv)) * norm);
+      }
+      for (int o = 16; o > 0; o >>= 1) loss += __shfl_xor_sync(0xffffffffu, loss, o);
+      if (best_i < 0 || loss < best) { best = loss; best_i = i; }
+    }
+    if (lane == 0 && best_i >= 0) scale[seg] = round_through<DT>(__fmul_rn(s0, __ldg(p + best_i)));
+  }
+}
+
 // ---------------------------------------------------------------- fp32 working copy
 template <typename T>
 __global__ void __launch_bounds__(256) to_fp32_kernel(const T* __restrict__ src, float* __restrict__ dst, int64_t n) {
@@ -261,6 +300,34 @@ extern "C" int mq_absmax_scales(const float* W, int64_t R, int64_t C, int64_t ld
       break;
     default:
       absmax_scales_kernel<MQ_F16><<<grid, 256, 0, st>>>(W, R, C, ldw, group, two_over_maxq, scale);
+  }
+  MQ_LAUNCH_CHECK();
+  return MQ_OK;
+}
+
+extern "C" int mq_mse_scales(const float* W, int64_t R, int64_t C, int64_t ldw, int64_t group, int bits, int out_dtype,
+                             const float* shrink, int n_shrink, float norm, float* scale, void* stream) {
+  using namespace mq;
+  MQ_REQUIRE(W && scale && shrink, MQ_ERR_ARGUMENT, "mq_mse_scales: null pointer");
+  MQ_REQUIRE(R > 0 && C > 0 && ldw >= C && n_shrink > 0, MQ_ERR_ARGUMENT, "mq_mse_scales: bad shape R=%lld C=%lld ldw=%lld n=%d",
+             (long long)R, (long long)C, (long long)ldw, n_shrink);
+  MQ_REQUIRE(group > 0 && C % group == 0, MQ_ERR_ARGUMENT, "mq_mse_scales: group %lld does not divide C=%lld",
+             (long long)group, (long long)C);
+  MQ_REQUIRE(bits >= 2 && bits <= 8, MQ_ERR_ARGUMENT, "mq_mse_scales: bits=%d", bits);
+  MQ_REQUIRE(valid_dtype(out_dtype), MQ_ERR_ARGUMENT, "mq_mse_scales: bad dtype %d", out_dtype);
+  const float maxq = (float)((1 << bits) - 1), zero = 0.5f * (float)(1 << bits);
+  const int64_t n_seg = R * (C / group);
+  const int grid = (int)(ceil_div(n_seg, 8) < 148 * 8 ? ceil_div(n_seg, 8) : 148 * 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (out_dtype) {
+    case MQ_F32:
+      mse_scales_kernel<MQ_F32><<<grid, 256, 0, st>>>(W, R, C, ldw, group, maxq, zero, shrink, n_shrink, norm, scale);
+      break;
+    case MQ_BF16:
+      mse_scales_kernel<MQ_BF16><<<grid, 256, 0, st>>>(W, R, C, ldw, group, maxq, zero, shrink, n_shrink, norm, scale);
+      break;
+    default:
+      mse_scales_kernel<MQ_F16><<<grid, 256, 0, st>>>(W, R, C, ldw, group, maxq, zero, shrink, n_shrink, norm, scale);
   }
   MQ_LAUNCH_CHECK();
   return MQ_OK;

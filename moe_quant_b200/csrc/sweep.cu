@@ -2,13 +2,16 @@
 // reference's captured loop (src/gptq_loop.py:141-148) with, per 128-column tile,
 // ONE sweep kernel plus ONE GEMM.
 //
-// Sweep kernel: a warp owns one weight row; lane l keeps columns 4l..4l+3 of the
-// current tile in registers.  Column j is quantized by the lane that owns it
+// Sweep kernel: eight lanes share one weight row, lane l keeps columns 16l..16l+15 of the
+// current tile in registers (four rows per warp).  Column j is quantized as
 //   q = clamp(floor(x/s + z + 0.5), 0, maxq)   y = round_to_dtype((q - z) s)   e = y - x
-// (src/gptq_loop.py:28-40, src/quant_utils.py:30-49), e is broadcast with one
-// shuffle and every lane applies  w_k += Uhat[j,k] e  to its columns k > j with the
-// row Uhat[j, tile] read from shared memory (src/gptq_loop.py:83-88).  Rows are
-// independent, so there is no synchronisation after the tile of Uhat is staged.
+// (src/gptq_loop.py:28-40, src/quant_utils.py:30-49) and its error is applied to the columns
+// behind it, w_k += Uhat[j,k] e (src/gptq_loop.py:83-88), with one fma per (j, k) in
+// increasing j: the reference's order.  The sixteen columns of a lane are a chain that needs
+// no communication (the lane applies each error to its own later columns at once), so the
+// tile is eight such chains back to back; after a chain its sixteen errors are broadcast with
+// shuffles and the other lanes of the row apply them to their columns.  Rows are independent:
+// no block-wide synchronisation after the tile of Uhat is staged in shared memory.
 //
 // The errors of the tile (R x 128) go to a scratch matrix and the lazy update
 //   W[:, later] += E Uhat[tile, later]             (src/gptq_loop.py:148)
@@ -22,141 +25,208 @@ namespace mq {
 namespace {
 
 constexpr int TILE = 128;
-constexpr int SWEEP_THREADS = 512;  // 16 rows per CTA
+constexpr int ROW_LANES = 8;                             // lanes that share one weight row
+constexpr int LANE_COLS = TILE / ROW_LANES;              // 16 consecutive columns per lane
+constexpr int SWEEP_THREADS = 128;                       // four warps of four rows
+constexpr int ROWS_PER_CTA = SWEEP_THREADS / ROW_LANES;  // 16
+// The tile of the factor in shared memory: row j holds eight chunks of 16 columns, 20 floats
+// apart, so that the eight lanes of a row read their chunks from disjoint groups of banks.
+constexpr int U_LANE_LD = LANE_COLS + 4;
+constexpr int U_ROW_LD = ROW_LANES * U_LANE_LD;          // 160 floats
+constexpr size_t kSweepSmem = (size_t)TILE * U_ROW_LD * sizeof(float);
 
-template <int DT>
-__global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(
-    const float* __restrict__ W, int64_t ldw, int R, const float* __restrict__ U, int64_t ldu,
-    const float* __restrict__ scale, const float* __restrict__ zero, int64_t group, int64_t s_rs, int64_t s_gs,
-    float maxq, float zero_default, uint8_t* __restrict__ codes, int64_t C,
-    typename StorageOf<DT>::type* __restrict__ deq, float* __restrict__ err, int i1, int nb,
-    const float* __restrict__ Worig, int64_t ldwo, uint16_t* __restrict__ err_planes, int64_t plane_stride,
-    int n_planes) {
+// eight codes below 16, held as bytes in two words (lowest byte = first column) -> one word of nibbles
+__device__ __forceinline__ uint32_t pack_nibbles(uint32_t lo4, uint32_t hi4) {
+  const uint32_t w = (lo4 & 0xFu) | ((lo4 >> 4) & 0xF0u) | ((lo4 >> 8) & 0xF00u) | ((lo4 >> 12) & 0xF000u);
+  const uint32_t v = (hi4 & 0xFu) | ((hi4 >> 4) & 0xF0u) | ((hi4 >> 8) & 0xF00u) | ((hi4 >> 12) & 0xF000u);
+  return w | (v << 16);
+}
+
+struct SweepArgs {
+  const float* W; int64_t ldw; int R;
+  const float* U; int64_t ldu;
+  const float* scale; const float* zero; int64_t group, s_rs, s_gs;
+  float maxq, zero_default;
+  uint8_t* codes; int64_t C;
+  int32_t* packed;   // optional (R, C/8) int32: the same codes, eight 4-bit nibbles per word
+  void* deq; float* err;
+  int i1, nb;
+  const float* Worig; int64_t ldwo;
+  uint16_t* err_planes; int64_t plane_stride; int n_planes;
+};
+
+// UNIFORM: the sixteen columns of a lane lie in one quantization group (group % 16 == 0).
+template <int DT, bool UNIFORM>
+__global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepArgs a) {
   using T = typename StorageOf<DT>::type;
-  extern __shared__ __align__(16) float ublk[];  // [TILE][TILE], strict upper triangle of the tile, 0 elsewhere
+  extern __shared__ __align__(16) float ublk[];  // [TILE][U_ROW_LD], strict upper triangle of the tile, 0 elsewhere
+  const int nb = a.nb, i1 = a.i1;
   // The factor is constant during the sweep: its tile is staged before this grid waits for the
   // rank-128 update that precedes it in the stream (only W depends on that update).
-  for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
-    int j = idx >> 5, k4 = (idx & 31) * 4;
+  for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += SWEEP_THREADS) {
+    const int j = idx >> 5, k4 = (idx & 31) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (j < nb && k4 < nb && k4 + 3 > j) {
-      v = __ldg(reinterpret_cast<const float4*>(U + (int64_t)(i1 + j) * ldu + i1 + k4));
+      v = __ldg(reinterpret_cast<const float4*>(a.U + (int64_t)(i1 + j) * a.ldu + i1 + k4));
       if (k4 + 0 <= j) v.x = 0.f;
       if (k4 + 1 <= j) v.y = 0.f;
       if (k4 + 2 <= j) v.z = 0.f;
     }
-    *reinterpret_cast<float4*>(&ublk[j * TILE + k4]) = v;
+    *reinterpret_cast<float4*>(&ublk[j * U_ROW_LD + (k4 >> 4) * U_LANE_LD + (k4 & 15)]) = v;
   }
   chain_wait();
   chain_release();
   __syncthreads();
 
-  const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * (SWEEP_THREADS / 32) + (threadIdx.x >> 5);
-  if (r >= R) return;
-  const int c0 = i1 + lane * 4;
-  const bool have = lane * 4 < nb;  // nb is a multiple of 4
-
-  float w[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {1.f, 1.f, 1.f, 1.f}, zr[4];
-#pragma unroll
-  for (int t = 0; t < 4; ++t) zr[t] = zero_default;
-  if (have) {
-    float4 v = *reinterpret_cast<const float4*>(W + (int64_t)r * ldw + c0);
-    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-    const int grp = (int)group;
-    if ((grp & 3) == 0) {
-      // the four columns of a lane share a group: one index, one 32-bit division
-      const int64_t off = (int64_t)r * s_rs + (int64_t)(c0 / grp) * s_gs;
-      const float s0 = __ldg(scale + off);
-      const float z0 = zero ? __ldg(zero + off) : zero_default;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) { sc[t] = s0; zr[t] = z0; }
-    } else {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int64_t off = (int64_t)r * s_rs + (int64_t)((c0 + t) / grp) * s_gs;
-        sc[t] = __ldg(scale + off);
-        if (zero) zr[t] = __ldg(zero + off);
-      }
-    }
-  }
-  float qv[4] = {0.f, 0.f, 0.f, 0.f}, yv[4] = {0.f, 0.f, 0.f, 0.f}, ev[4] = {0.f, 0.f, 0.f, 0.f};
+  const int sub = threadIdx.x & (ROW_LANES - 1);   // this lane's chunk of the row
+  const int c_local = sub * LANE_COLS;
+  const int c0 = i1 + c_local;
+  const float maxq = a.maxq;
   // Inverse-free form (Worig != nullptr): U is the unit factor Utilde = Uhat^-1 and what is
   // propagated is minus the total change of the column, -(y - w_original), instead of the
   // error against the running value; x_j = w_j - sum_{i<j} (y_i - w_i) Utilde[i,j] is the same
   // number as the reference's running weight (E Uhat = Y - W  <=>  E = (Y - W) Utilde).
-  const bool inverse_free = Worig != nullptr;
-  float wo[4] = {0.f, 0.f, 0.f, 0.f};
-  if (inverse_free && have) {
-    float4 v = *reinterpret_cast<const float4*>(Worig + (int64_t)r * ldwo + c0);
-    wo[0] = v.x; wo[1] = v.y; wo[2] = v.z; wo[3] = v.w;
-  }
+  const bool inverse_free = a.Worig != nullptr;
+  const int n_owner = (nb + LANE_COLS - 1) / LANE_COLS;
 
-  // x / s through the reciprocal and one correction step (the final stage of a correctly rounded
-  // division): a few FMAs on the serial chain instead of the full division sequence.
-  float rs[4];
+  // whole warps iterate together (the shuffles below are warp-wide); rows past R carry zeros
+  for (int r_warp = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5) * 4; r_warp < a.R; r_warp += gridDim.x * ROWS_PER_CTA) {
+    const int r = r_warp + ((threadIdx.x & 31) >> 3);
+    const bool valid = r < a.R;
+    float w[LANE_COLS], wo[LANE_COLS];
 #pragma unroll
-  for (int t = 0; t < 4; ++t) rs[t] = 1.0f / sc[t];
+    for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f), vo = v;
+      if (valid && c_local + 4 * qd < nb) {
+        v = *reinterpret_cast<const float4*>(a.W + (int64_t)r * a.ldw + c0 + 4 * qd);
+        if (inverse_free) vo = *reinterpret_cast<const float4*>(a.Worig + (int64_t)r * a.ldwo + c0 + 4 * qd);
+      }
+      w[4 * qd] = v.x; w[4 * qd + 1] = v.y; w[4 * qd + 2] = v.z; w[4 * qd + 3] = v.w;
+      wo[4 * qd] = vo.x; wo[4 * qd + 1] = vo.y; wo[4 * qd + 2] = vo.z; wo[4 * qd + 3] = vo.w;
+    }
+    // grid of the lane's columns; x / s goes through the reciprocal and one correction step (the
+    // final stage of a correctly rounded division): a few FMAs on the serial chain instead of
+    // the full division sequence
+    constexpr int NS = UNIFORM ? 1 : LANE_COLS;
+    float sc[NS], zr[NS], rs[NS];
+#pragma unroll
+    for (int t = 0; t < NS; ++t) {
+      sc[t] = 1.0f;
+      zr[t] = a.zero_default;
+      if (valid && c_local + t < nb) {
+        const int64_t off = (int64_t)r * a.s_rs + (int64_t)((c0 + t) / a.group) * a.s_gs;
+        sc[t] = __ldg(a.scale + off);
+        if (a.zero) zr[t] = __ldg(a.zero + off);
+      }
+      rs[t] = 1.0f / sc[t];
+    }
 
-  const int n_quads = nb >> 2;
-  for (int jq = 0; jq < n_quads; ++jq) {
-    // The four columns of quad jq belong to lane jq and depend on each other only through the
-    // 4 x 4 diagonal block of U, so that lane can run them back to back without a shuffle.  Every
-    // lane runs the same four steps on a copy of its own values against that block (uniform
-    // code, no divergence); only lane jq's results are real.  Its four errors are then broadcast
-    // and applied to the true running weights of all lanes, in the same order, with the same
-    // FMAs the one-column-at-a-time recurrence would use.
-    float wl[4] = {w[0], w[1], w[2], w[3]};
-    float e4[4];
-    const float* ud = &ublk[(jq * 4) * TILE + jq * 4];  // diagonal block, same address for all lanes
+#pragma unroll 1
+    for (int lo = 0; lo < n_owner; ++lo) {
+      // Chain of the sixteen columns that lane `lo` of every row owns.  Every lane runs the same
+      // sixteen steps on a copy of its own values against that lane's diagonal 16 x 16 block
+      // (uniform code, one shared-memory address per load for the whole warp); only lane lo's
+      // results are real.
+      const float* ud = &ublk[(lo * LANE_COLS) * U_ROW_LD + lo * U_LANE_LD];
+      float wl[LANE_COLS], e[LANE_COLS];
+      uint32_t qp[LANE_COLS / 4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float x = wl[t];
-      float d = x * rs[t];
-      d = fmaf(fmaf(-sc[t], d, x), rs[t], d);
-      const float q = fminf(fmaxf(floorf((d + zr[t]) + 0.5f), 0.0f), maxq);
-      const float y = round_through<DT>((q - zr[t]) * sc[t]);
-      const float e = inverse_free ? (wo[t] - y) : (y - x);
-      e4[t] = e;
-      if (lane == jq) { qv[t] = q; yv[t] = y; ev[t] = e; }
+      for (int t = 0; t < LANE_COLS; ++t) wl[t] = w[t];
 #pragma unroll
-      for (int t2 = t + 1; t2 < 4; ++t2) wl[t2] = fmaf(ud[t * TILE + t2], e, wl[t2]);
-    }
+      for (int t = 0; t < LANE_COLS; ++t) {
+        const float s_t = sc[UNIFORM ? 0 : t], z_t = zr[UNIFORM ? 0 : t], r_t = rs[UNIFORM ? 0 : t];
+        const float x = wl[t];
+        float d = x * r_t;
+        d = fmaf(fmaf(-s_t, d, x), r_t, d);
+        const float q = fminf(fmaxf(floorf((d + z_t) + 0.5f), 0.0f), maxq);
+        const float y = round_through<DT>((q - z_t) * s_t);
+        const float et = inverse_free ? (wo[t] - y) : (y - x);
+        e[t] = et;
+        qp[t >> 2] |= (uint32_t)q << (8 * (t & 3));
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float eb = __shfl_sync(0xffffffffu, e4[t], jq);
-      const float4 u = *reinterpret_cast<const float4*>(&ublk[(jq * 4 + t) * TILE + lane * 4]);
-      w[0] = fmaf(u.x, eb, w[0]);
-      w[1] = fmaf(u.y, eb, w[1]);
-      w[2] = fmaf(u.z, eb, w[2]);
-      w[3] = fmaf(u.w, eb, w[3]);
+        for (int t2 = t + 1; t2 < LANE_COLS; ++t2) wl[t2] = fmaf(ud[t * U_ROW_LD + t2], et, wl[t2]);
+      }
+      if (sub == lo && valid) {
+        // this lane's sixteen columns are final: codes, optional dequantized values, errors
+#pragma unroll
+        for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
+          if (c_local + 4 * qd >= nb) continue;
+          *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.C + c0 + 4 * qd) = qp[qd];
+          // the compressed-tensors word of columns 8k..8k+7 (column 8k+i at bits 4i..4i+3), written
+          // here so that no separate packing pass has to read the codes back
+          if (a.packed && (qd & 1)) a.packed[(int64_t)r * (a.C >> 3) + ((c0 + 4 * qd) >> 3)] = (int32_t)pack_nibbles(qp[qd - 1], qp[qd]);
+          if (a.deq) {
+            T* dq = static_cast<T*>(a.deq) + (int64_t)r * a.C + c0 + 4 * qd;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float qf = (float)((qp[qd] >> (8 * t)) & 0xFFu);
+              dq[t] = from_float<T>((qf - zr[UNIFORM ? 0 : 4 * qd + t]) * sc[UNIFORM ? 0 : 4 * qd + t]);
+            }
+          }
+        }
+        // columns past nb of a narrow last tile hold zeros so that the GEMM may read all 128
+        if (a.err_planes) {
+          // the tensor-core update reads the errors as bf16 planes: write them in that form directly
+          uint32_t hp[LANE_COLS / 2], mp[LANE_COLS / 2], lp[LANE_COLS / 2];
+#pragma unroll
+          for (int t = 0; t < LANE_COLS; t += 2) {
+            uint16_t h0, m0, l0, h1, m1, l1;
+            split_bf16x3(e[t], h0, m0, l0);
+            split_bf16x3(e[t + 1], h1, m1, l1);
+            hp[t >> 1] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+            mp[t >> 1] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+            lp[t >> 1] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+          }
+          uint16_t* dst = a.err_planes + (int64_t)r * TILE + c_local;
+          reinterpret_cast<uint4*>(dst)[0] = make_uint4(hp[0], hp[1], hp[2], hp[3]);
+          reinterpret_cast<uint4*>(dst)[1] = make_uint4(hp[4], hp[5], hp[6], hp[7]);
+          if (a.n_planes > 1) {
+            reinterpret_cast<uint4*>(dst + a.plane_stride)[0] = make_uint4(mp[0], mp[1], mp[2], mp[3]);
+            reinterpret_cast<uint4*>(dst + a.plane_stride)[1] = make_uint4(mp[4], mp[5], mp[6], mp[7]);
+          }
+          if (a.n_planes > 2) {
+            reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[0] = make_uint4(lp[0], lp[1], lp[2], lp[3]);
+            reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[1] = make_uint4(lp[4], lp[5], lp[6], lp[7]);
+          }
+        } else {
+          float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * TILE + c_local);
+#pragma unroll
+          for (int qd = 0; qd < LANE_COLS / 4; ++qd) dst[qd] = make_float4(e[4 * qd], e[4 * qd + 1], e[4 * qd + 2], e[4 * qd + 3]);
+        }
+      }
+      // The sixteen errors of lane lo reach the other lanes of the row, which apply them to their
+      // own columns in the same order, with the same FMAs, as a one-column-at-a-time recurrence.
+      // (For the lanes in front of lo the staged factor holds zeros; lane lo's own values are
+      // not needed any more.)
+#pragma unroll
+      for (int t = 0; t < LANE_COLS; ++t) {
+        const float eb = __shfl_sync(0xffffffffu, e[t], lo, ROW_LANES);
+        const float4* up = reinterpret_cast<const float4*>(&ublk[(lo * LANE_COLS + t) * U_ROW_LD + sub * U_LANE_LD]);
+#pragma unroll
+        for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
+          const float4 u = up[qd];
+          w[4 * qd] = fmaf(u.x, eb, w[4 * qd]);
+          w[4 * qd + 1] = fmaf(u.y, eb, w[4 * qd + 1]);
+          w[4 * qd + 2] = fmaf(u.z, eb, w[4 * qd + 2]);
+          w[4 * qd + 3] = fmaf(u.w, eb, w[4 * qd + 3]);
+        }
+      }
     }
   }
-  if (have) {
-    uchar4 qc = make_uchar4((unsigned char)qv[0], (unsigned char)qv[1], (unsigned char)qv[2], (unsigned char)qv[3]);
-    *reinterpret_cast<uchar4*>(codes + (int64_t)r * C + c0) = qc;
-    if (deq) {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) deq[(int64_t)r * C + c0 + t] = from_float<T>(yv[t]);
-    }
-  }
-  // columns past nb of a narrow last tile hold zeros so the GEMM may read all 128
-  if (err_planes) {
-    // the tensor-core update reads the errors as bf16 planes: write them in that form directly
-    uint16_t h[4], m[4], l[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) split_bf16x3(ev[t], h[t], m[t], l[t]);
-    uint16_t* dst = err_planes + (int64_t)r * TILE + lane * 4;
-    *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
-    if (n_planes > 1)
-      *reinterpret_cast<uint2*>(dst + plane_stride) =
-          make_uint2((uint32_t)m[0] | ((uint32_t)m[1] << 16), (uint32_t)m[2] | ((uint32_t)m[3] << 16));
-    if (n_planes > 2)
-      *reinterpret_cast<uint2*>(dst + 2 * plane_stride) =
-          make_uint2((uint32_t)l[0] | ((uint32_t)l[1] << 16), (uint32_t)l[2] | ((uint32_t)l[3] << 16));
-  } else {
-    *reinterpret_cast<float4*>(err + (int64_t)r * TILE + lane * 4) = make_float4(ev[0], ev[1], ev[2], ev[3]);
-  }
+}
+
+template <int DT>
+int launch_sweep_tile(bool chained, bool uniform, int grid, cudaStream_t st, const SweepArgs& args) {
+  if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true>, dim3(grid), dim3(SWEEP_THREADS), kSweepSmem, st, args));
+  else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false>, dim3(grid), dim3(SWEEP_THREADS), kSweepSmem, st, args));
+  return MQ_OK;
+}
+
+template <int DT>
+int configure_dtype() {
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
+  return MQ_OK;
 }
 
 int configure_once() {
@@ -164,10 +234,9 @@ int configure_once() {
   int dev = 0;
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
-    const int bytes = TILE * TILE * (int)sizeof(float);
-    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<MQ_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    MQ_TRY(configure_dtype<MQ_F32>());
+    MQ_TRY(configure_dtype<MQ_BF16>());
+    MQ_TRY(configure_dtype<MQ_F16>());
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -184,7 +253,7 @@ size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
                const float* zero, int64_t group, int64_t s_rs, int64_t s_gs, int bits, int out_dtype, uint8_t* codes,
                void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st,
-               const float* col_div) {
+               const float* col_div, int32_t* packed) {
   // col_div (tensor math only): above its diagonal 128-blocks Uhat holds the factor before its
   // columns were divided by col_div; the plane split divides where it reads it.  The diagonal
   // blocks, which the tiles read, are already scaled.
@@ -209,33 +278,35 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   }
   uint16_t* const ep_arg = tensor ? err_set.base : nullptr;
   const int64_t ep_stride = tensor ? err_set.total_rows * TILE : 0;
-  const float maxq = (float)((1 << bits) - 1);
-  const float zero_default = 0.5f * (float)(1 << bits);
-  const int grid = (int)ceil_div(R, SWEEP_THREADS / 32);
-  const size_t smem = TILE * TILE * sizeof(float);
+  SweepArgs sa;
+  sa.W = W; sa.ldw = ldw; sa.R = (int)R;
+  sa.U = Uhat; sa.ldu = ldu;
+  sa.scale = scale; sa.zero = zero; sa.group = group; sa.s_rs = s_rs; sa.s_gs = s_gs;
+  sa.maxq = (float)((1 << bits) - 1);
+  sa.zero_default = 0.5f * (float)(1 << bits);
+  sa.codes = codes; sa.C = C;
+  sa.packed = packed;
+  sa.deq = deq; sa.err = err;
+  sa.Worig = Worig; sa.ldwo = ldwo;
+  sa.err_planes = ep_arg; sa.plane_stride = ep_stride; sa.n_planes = split;
+  const bool uniform = group % LANE_COLS == 0;
+  // every CTA stages the tile of the factor once and then walks row groups: no more CTAs than
+  // two per SM, so that a tall layer does not stage the same tile thousands of times
+  const int64_t row_groups = ceil_div(R, ROWS_PER_CTA);
+  const int grid = (int)(row_groups < 2 * 148 ? row_groups : 2 * 148);
   for (int64_t i1 = 0; i1 < C; i1 += TILE) {
     const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
-    // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
     {
     // The kernel stages its tile of the factor before it waits for its predecessor: only a launch
     // that follows this loop's own update (which writes W, never the factor) may be chained.
     const bool chained = i1 > 0;
+    // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
     ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
+    sa.i1 = (int)i1; sa.nb = nb;
     switch (out_dtype) {
-      case MQ_F32:
-        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F32>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
-                                                                  maxq, zero_default, codes, C, static_cast<float*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
-        break;
-      case MQ_BF16:
-        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_BF16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
-                                                                   maxq, zero_default, codes, C,
-                                                                   static_cast<__nv_bfloat16*>(deq), err, (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
-        break;
-      default:
-        MQ_CUDA(launch_chained(chained, sweep_tile_kernel<MQ_F16>, dim3(grid), dim3(SWEEP_THREADS), smem, st, W, ldw, (int)R, Uhat, ldu, scale, zero, group, s_rs, s_gs,
-                                                                  maxq, zero_default, codes, C, static_cast<__half*>(deq), err,
-                                                                  (int)i1, nb, Worig, ldwo, ep_arg, ep_stride, split));
+      case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
+      case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
+      default: MQ_TRY(launch_sweep_tile<MQ_F16>(chained, uniform, grid, st, sa));
     }
     }
     MQ_LAUNCH_CHECK();
@@ -269,7 +340,7 @@ extern "C" size_t mq_gptq_sweep_workspace_bytes(int64_t R, int64_t C, int math, 
 
 extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu,
                              const float* scale, const float* zero, int64_t group, int64_t row_stride,
-                             int64_t group_stride, int bits, int out_dtype, uint8_t* codes, void* dequantized,
+                             int64_t group_stride, int bits, int out_dtype, uint8_t* codes, int32_t* packed, void* dequantized,
                              const float* W_original, int64_t ldwo, int math, int split, void* workspace,
                              size_t workspace_bytes, void* stream) {
   using namespace mq;
@@ -289,6 +360,8 @@ extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const 
     MQ_REQUIRE(ldwo >= C && ldwo % 4 == 0 && aligned(W_original, 16) && W_original != W, MQ_ERR_ALIGNMENT,
                "mq_gptq_sweep: W_original must be a separate 16-byte aligned matrix with ldwo %% 4 == 0");
   }
+  MQ_REQUIRE(!packed || (bits == 4 && !zero && aligned(packed, 4)), MQ_ERR_UNSUPPORTED,
+             "mq_gptq_sweep: packed words need bits == 4, the symmetric zero point and a 4-byte aligned buffer");
   return gptq_sweep(W, R, C, ldw, Uhat, ldu, scale, zero, group, row_stride, group_stride, bits, out_dtype, codes,
-                    dequantized, W_original, ldwo, math, split, ws, static_cast<cudaStream_t>(stream), nullptr);
+                    dequantized, W_original, ldwo, math, split, ws, static_cast<cudaStream_t>(stream), nullptr, packed);
 }

@@ -242,7 +242,32 @@ class GPTQ:
             dist.broadcast(zero, src=0)
         return qweight, scale, zero
 
+    def _mse_search(self) -> bool:
+        """True when the scales are refined by the shrink-factor search.  The reference compares
+        the stored value with the Enum member (src/quant_utils.py:218), and its driver stores the
+        command-line STRING (quant.py:270): "mse" as a string therefore means absmax there, and
+        means absmax here.  Passing QuantizationScale.MSE itself switches the search on."""
+        from .quant_utils import QuantizationScale
+        return self.quantization_scale == QuantizationScale.MSE
+
+    def _quantize_mse(self, bits: int, g: int) -> Tuple[Tensor, Tensor]:
+        """Default column order with MSE-refined scales: the stages of the fused entry point one
+        by one, with the search between the absmax grid and the sweep."""
+        W = self._weight_2d()
+        Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
+        self._prepare_shared_hessian(Wf)
+        scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
+        ops.mse_scales(Wf, scale, g, bits, self.W_dtype)
+        U = self.H.clone()
+        flags, _ = ops.chol_unit_factor(U, self.precision)
+        self._absorb_flags(flags)
+        codes, _ = ops.gptq_sweep(Wf.clone(), U, scale, None, g, self.d_col // g, 1, bits, self.W_dtype,
+                                  precision=self.precision, W_original=Wf)
+        return codes, scale
+
     def _quantize_default(self, bits: int, g: int) -> Tuple[Tensor, Tensor]:
+        if self._mse_search():
+            return self._quantize_mse(bits, g)
         W = self._weight_2d()
         shares_hessian = self.num_tied_handles > 0 or self.tied_gptq_handle is not None
         if not shares_hessian:
@@ -282,6 +307,8 @@ class GPTQ:
         Wf = W.float().contiguous() if W.dtype != torch.float32 else W.clone().contiguous()
         self._prepare_shared_hessian(Wf)
         scale = ops.absmax_scales(Wf, g, bits, self.W_dtype)
+        if self._mse_search():
+            ops.mse_scales(Wf, scale, g, bits, self.W_dtype)
         perm = torch.argsort(self.H.diag(), descending=True)
         Hp = self.H[perm][:, perm].contiguous()
         U, flags, _ = ops.hinv_upper(Hp, self.precision)
@@ -296,6 +323,33 @@ class GPTQ:
     def quantize(self, bits: int | float) -> Tuple[Tensor, Tensor, Tensor]:
         self.quantization_pre_step()
         return self._quantize(int(bits))
+
+    @torch.no_grad()
+    def quantize_packed(self, bits: int | float) -> dict:
+        """quantize(bits) and pack_weight (pack_quantized_model.py:57-75) in one pass: the column
+        sweep writes the int32 words of the compressed-tensors layout next to the uint8 codes, so
+        the codes are never read back by a packing kernel.  Returns the three tensors of
+        quantize() and the three of pack_weight():
+            qweight, scale, zero, weight_packed (R, C/8) int32, weight_shape int64 [R, C], weight_scale.
+        Handles on another route (tied, distributed, activation order, MSE scales) pack in a
+        second pass; the result is the same."""
+        bits = int(bits)
+        fused = (bits == 4 and self.sym and not self.is_distributed and self.tied_gptq_handle is None
+                 and self.num_tied_handles == 0 and self.quantization_order == QuantizationOrder.DEFAULT
+                 and not self._mse_search() and self.d_col % 8 == 0)
+        self.quantization_pre_step()
+        if fused:
+            codes, scales, _, flags, packed = ops.quantize_layer([self._weight_2d()], self.H, self._group(), bits,
+                                                                 self.rel_damp, precision=self.precision, want_packed=True)
+            self._hessian_ready = True
+            self._absorb_flags(flags)
+            qweight, scale, words = codes[0], scales[0].to(self.W_dtype), packed[0]
+            zero = torch.full_like(scale, (2 ** bits) / 2)
+        else:
+            qweight, scale, zero = self._quantize(bits)
+            words = ops.pack_int4(qweight)
+        return {"qweight": qweight, "scale": scale, "zero": zero, "weight_packed": words,
+                "weight_shape": torch.tensor([self.d_row, self.d_col]), "weight_scale": scale}
 
     @torch.no_grad()
     def _get_hessian_inverse(self) -> Tensor:
@@ -357,7 +411,7 @@ def quantize_tied(handles: Sequence[GPTQ], bits: int) -> List[Tuple[Tensor, Tens
     for h in handles[1:]:
         if h.tied_gptq_handle is not owner:
             raise MoeQuantError("quantize_tied: every handle after the first must be tied to the first")
-    if owner.quantization_order != QuantizationOrder.DEFAULT or not owner.sym:
+    if owner.quantization_order != QuantizationOrder.DEFAULT or not owner.sym or any(h._mse_search() for h in handles):
         return [h.quantize(bits) for h in handles]
     owner.quantization_pre_step()
     for h in handles[1:]:

@@ -155,6 +155,21 @@ def absmax_scales(W: Tensor, group: int, bits: int, dtype: torch.dtype) -> Tenso
     return out
 
 
+def mse_scales(W: Tensor, scale: Tensor, group: int, bits: int, dtype: torch.dtype, max_shrink: float = 0.2,
+               n_grid: int = 100, norm: float = 2.4) -> Tensor:
+    """Refines absmax scales (R, C/group) in place by the reference's shrink-factor search and returns them."""
+    require_cuda(W, "W")
+    require_cuda(scale, "scale")
+    if W.dtype != torch.float32 or W.stride(1) != 1 or scale.dtype != torch.float32 or not scale.is_contiguous():
+        raise MoeQuantError("W must be fp32 with unit column stride, scale contiguous fp32")
+    R, C = W.shape
+    shrink = torch.linspace(1, max_shrink, n_grid, dtype=torch.float32, device=W.device)   # src/quant_utils.py:219
+    with torch.cuda.device(W.device):
+        check(lib().mq_mse_scales(ptr(W), R, C, W.stride(0), group, bits, dtype_code(dtype), ptr(shrink), n_grid, norm,
+                                  ptr(scale), stream_ptr(W.device)))
+    return scale
+
+
 def chol_unit_factor(H: Tensor, precision: Optional[Precision] = None, flags: Optional[Tensor] = None):
     """In place: damped H -> Utilde = T diag(T)^-1 (unit upper), H = T T^T.  Returns (flags, diag(T))."""
     p = _prec(precision)
@@ -174,11 +189,12 @@ def chol_unit_factor(H: Tensor, precision: Optional[Precision] = None, flags: Op
 
 def gptq_sweep(W: Tensor, Uhat: Tensor, scale: Tensor, zero: Optional[Tensor], group: int, row_stride: int,
                group_stride: int, bits: int, dtype: torch.dtype, want_dequantized: bool = False,
-               precision: Optional[Precision] = None, W_original: Optional[Tensor] = None
-               ) -> Tuple[Tensor, Optional[Tensor]]:
+               precision: Optional[Precision] = None, W_original: Optional[Tensor] = None,
+               packed_out: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
     """Column sweep over the fp32 working copy W (R, C), which is destroyed.
     With W_original (a second fp32 copy of the weights) `Uhat` must be the unit factor from
     chol_unit_factor and the inverse-free recurrence is used.
+    packed_out: optional (R, C/8) int32 tensor that receives the compressed-tensors words.
     Returns (codes uint8 (R, C), dequantized (R, C) of `dtype` or None)."""
     p = _prec(precision)
     for t, n in ((W, "W"), (Uhat, "Uhat"), (scale, "scale")):
@@ -193,19 +209,20 @@ def gptq_sweep(W: Tensor, Uhat: Tensor, scale: Tensor, zero: Optional[Tensor], g
     ws = _lib.workspace(W.device, nbytes)
     with torch.cuda.device(W.device):
         check(L.mq_gptq_sweep(ptr(W), R, C, W.stride(0), ptr(Uhat), Uhat.stride(0), ptr(scale), ptr(zero), group,
-                              row_stride, group_stride, bits, dtype_code(dtype), ptr(codes), ptr(deq),
+                              row_stride, group_stride, bits, dtype_code(dtype), ptr(codes), ptr(packed_out), ptr(deq),
                               ptr(W_original), 0 if W_original is None else W_original.stride(0), p.math,
                               p.split_sweep, ptr(ws), ws.numel(), stream_ptr(W.device)))
     return codes, deq
 
 
 def quantize_layer(weights: Sequence[Tensor], H: Tensor, group: int, bits: int, rel_damp: float,
-                   want_dequantized: bool = False, precision: Optional[Precision] = None):
+                   want_dequantized: bool = False, precision: Optional[Precision] = None, want_packed: bool = False):
     """GPTQ.quantize for one layer or for several layers that share H.
 
     weights: (R, C) tensors of one dtype; H (C, C) fp32 is damped in place.
     Returns (list of codes uint8 (R, C), list of scales fp32 (R, C/group),
-             list of dequantized or None, flags int32[4] on the device).
+             list of dequantized or None, flags int32[4] on the device); with want_packed a fifth
+    element, the list of (R, C/8) int32 compressed-tensors words written by the sweep itself.
     """
     p = _prec(precision)
     require_cuda(H, "H")
@@ -222,6 +239,7 @@ def quantize_layer(weights: Sequence[Tensor], H: Tensor, group: int, bits: int, 
     codes = [torch.empty(R, C, dtype=torch.uint8, device=dev) for _ in range(n)]
     scales = [torch.empty(R, C // group, dtype=torch.float32, device=dev) for _ in range(n)]
     deqs = [torch.empty(R, C, dtype=dtype, device=dev) for _ in range(n)] if want_dequantized else None
+    packed = [torch.empty(R, C // 8, dtype=torch.int32, device=dev) for _ in range(n)] if want_packed else None
     flags = _flags_tensor(dev)
     L = lib()
     nbytes = L.mq_quantize_layer_workspace_bytes(n, R, C, p.math, p.split_hinv, p.split_sweep)
@@ -231,10 +249,13 @@ def quantize_layer(weights: Sequence[Tensor], H: Tensor, group: int, bits: int, 
     c_arr = arr(*[t.data_ptr() for t in codes])
     s_arr = arr(*[t.data_ptr() for t in scales])
     d_arr = arr(*[t.data_ptr() for t in deqs]) if deqs is not None else None
+    p_arr = arr(*[t.data_ptr() for t in packed]) if packed is not None else None
     with torch.cuda.device(dev):
         check(L.mq_quantize_layer(w_arr, dtype_code(dtype), n, R, C, ptr(H), H.stride(0), group, bits, rel_damp, c_arr,
-                                  s_arr, d_arr, ptr(flags), p.math, p.split_hinv, p.split_sweep, ptr(ws), ws.numel(),
+                                  p_arr, s_arr, d_arr, ptr(flags), p.math, p.split_hinv, p.split_sweep, ptr(ws), ws.numel(),
                                   stream_ptr(dev)))
+    if want_packed:
+        return codes, scales, deqs, flags, packed
     return codes, scales, deqs, flags
 
 

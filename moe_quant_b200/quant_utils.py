@@ -42,6 +42,12 @@ def get_quantization_grid(weight: Tensor, group_size: int, bits: int, symmetric:
         raise MoeQuantError("only the symmetric grid is implemented")
     W = weight.float().contiguous()
     scale = ops.absmax_scales(W, group_size, bits, dtype if dtype is not None else torch.float32)
+    # Like the reference, the search runs only for the Enum member: a plain string "mse" (what
+    # GPTQ stores when quant.py passes its command-line value) compares unequal and gives absmax.
+    if quantization_scale == QuantizationScale.MSE:
+        ops.mse_scales(W, scale, group_size, bits, dtype if dtype is not None else torch.float32,
+                       _unused.get("quant_max_shrink", 0.2), _unused.get("quant_n_grid", 100),
+                       _unused.get("quant_norm", 2.4))
     maxq = torch.tensor(2 ** bits - 1, dtype=W.dtype, device=W.device)
     zero = torch.full_like(scale, (2 ** bits) / 2)
     return scale.repeat_interleave(group_size, dim=-1), zero.repeat_interleave(group_size, dim=-1), maxq

@@ -5,8 +5,10 @@ reference's key names, plus the `quantization_config` block that goes into confi
 """
 from __future__ import annotations
 
+import json
 import os
-from typing import Dict, Iterable, Optional
+from collections import defaultdict
+from typing import Dict, Iterable, Mapping, Optional
 
 import torch
 from safetensors.torch import save_file
@@ -58,3 +60,51 @@ def pack_saved_layers(quantized_model_path: str, layer_names: Iterable[str], out
     os.makedirs(os.path.dirname(os.path.abspath(out_file)), exist_ok=True)
     save_file(state, out_file)
     return state
+
+
+def pack_model(quantized_model_path: str, packed_model_path: str, num_blocks: int,
+               block_tensors: Optional[Mapping[int, Dict[str, torch.Tensor]]] = None,
+               head_tensors: Optional[Dict[str, torch.Tensor]] = None,
+               tail_tensors: Optional[Dict[str, torch.Tensor]] = None,
+               config: Optional[dict] = None, sym: bool = True) -> Dict[str, str]:
+    """The output side of pack_quantized_model.py:136-235 for a model whose layers were saved as
+    `<quantized_model_path>/model.layers.<i>.<...>/quantized_weight.pt` together with
+    `metadata.pt` ({'bits', 'group_size', 'quantize_only_experts'}, quant.py:430-440).
+
+    One shard per transformer block, numbered like the reference (`model-00001` holds the
+    embeddings = head_tensors, blocks follow, the last shard holds lm_head and the final norm =
+    tail_tensors; `num_blocks + 2` shards in all), `model.safetensors.index.json` with the weight
+    map, and `config.json` carrying the `quantization_config` block.  block_tensors[i] are the
+    unquantized parameters of block i (norms, router, ...), already in their final dtype; the
+    original checkpoint's FP8 ingest is not part of this path.  Returns the weight map."""
+    meta = torch.load(os.path.join(quantized_model_path, "metadata.pt"), weights_only=True)
+    bits, group_size = int(meta["bits"]), meta["group_size"]
+    names = defaultdict(list)
+    for layer_name in sorted(os.listdir(quantized_model_path)):
+        if os.path.isdir(os.path.join(quantized_model_path, layer_name)):
+            names[int(layer_name.split(".")[2])].append(layer_name)          # pack_quantized_model.py:143-146
+    os.makedirs(packed_model_path, exist_ok=True)
+    n_shards = num_blocks + 2
+    index: Dict[str, str] = {}
+
+    def shard(i: int) -> str:
+        return f"model-{i:05}-of-{n_shards:05}.safetensors"
+
+    if head_tensors:
+        save_file({k: v.contiguous() for k, v in head_tensors.items()}, os.path.join(packed_model_path, shard(1)))
+        index.update({k: shard(1) for k in head_tensors})
+    for b in range(num_blocks):
+        state = pack_saved_layers(quantized_model_path, names.get(b, []), os.path.join(packed_model_path, shard(b + 2)),
+                                  bits, group_size, sym, (block_tensors or {}).get(b))
+        index.update({k: shard(b + 2) for k in state})
+    if tail_tensors:
+        save_file({k: v.contiguous() for k, v in tail_tensors.items()}, os.path.join(packed_model_path, shard(n_shards)))
+        index.update({k: shard(n_shards) for k in tail_tensors})
+    with open(os.path.join(packed_model_path, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": index}, f)                  # pack_quantized_model.py:229-230
+    cfg = dict(config or {})
+    cfg.pop("quantization_config", None)
+    cfg["quantization_config"] = quantization_config(bits, group_size, bool(meta.get("quantize_only_experts", False)))
+    with open(os.path.join(packed_model_path, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=2)
+    return index

@@ -100,6 +100,30 @@ def symmetric_grid(W: Tensor, group_size: int, bits: int, dtype: Optional[torch.
     return scale, zero, float(maxq)
 
 
+def mse_scale(Wg: Tensor, scale: Tensor, zero: Tensor, maxq: float, dtype: Optional[torch.dtype],
+              max_shrink: float = 0.2, n_grid: int = 100, norm: float = 2.4) -> Tensor:
+    """Shrink-factor search of ``mse_scale_triton_kernel`` (src/quant_utils.py:104-139) with the
+    candidates of ``get_quantization_grid`` (``:219``).  Wg (R, G, g) fp32; scale, zero (R, G).
+
+    Per candidate p_i: s_i = round_fp(scale * p_i); the group is quantized with the Triton
+    rounding (floor(x/s + z + 0.5), ``:30-34``) and dequantized through the dtype; the loss is
+    sum |q - x|^norm with the power taken as exp(norm * log|.|) (``tl_pow``, ``:25-27``); the scale
+    becomes round_fp(scale * p_argmin).  The reference pads the candidate axis to 128 with an
+    unmasked load of unspecified values; only the real candidates are searched here."""
+    p = torch.linspace(1, max_shrink, n_grid, dtype=Wg.dtype)
+    best = torch.full_like(scale, float("inf"))
+    best_i = torch.zeros_like(scale, dtype=torch.long)
+    for i in range(n_grid):
+        s = round_fp(scale * p[i], dtype)[..., None]
+        q = torch.clamp(torch.floor((Wg / s + zero[..., None]) + 0.5), 0.0, maxq)
+        y = round_fp((q - zero[..., None]) * s, dtype)
+        loss = ((y - Wg).abs().log() * norm).exp().sum(-1)
+        better = loss < best
+        best = torch.where(better, loss, best)
+        best_i = torch.where(better, torch.full_like(best_i, i), best_i)
+    return round_fp(scale * p[best_i], dtype)
+
+
 # ----------------------------------------------------------------------------
 # Hessian inverse              src/gptq.py:220-243, src/linalg_utils.py:8-12
 # ----------------------------------------------------------------------------
@@ -193,6 +217,7 @@ def quantize_layer(
     rel_damp: float = 1e-2,
     block_size: Optional[int] = None,
     act_order: bool = False,
+    mse: bool = False,
 ):
     """``GPTQ.quantize(bits)`` for a symmetric, non-distributed, untied handle.
 
@@ -205,6 +230,8 @@ def quantize_layer(
     block = block_size or C
     H, W, zero_samples, nan = pre_step(H, weight)
     scale, zero, maxq = symmetric_grid(W, g, bits, dtype)
+    if mse:
+        scale = mse_scale(W.unflatten(-1, (-1, g)), scale, zero, maxq, dtype)
     if act_order:
         perm = torch.argsort(H.diag(), descending=True)
     else:

@@ -13,7 +13,10 @@ number it stores comes out of the reference's modules imported UNCHANGED and run
   * ``<case>.qweight`` / ``<case>.scale``: the whole ``src.gptq.GPTQ`` handle on the device
     (cuBLAS Hessian, cuSOLVER factorisations, Triton sweep) fed with the fixture's batches;
   * ``mid_*``: two larger layers (several GPTQ blocks, hundreds of tokens) whose inputs are
-    stored here as well, with the handle's ``Uhat`` so that the sweep can be replayed alone.
+    stored here as well, with the handle's ``Uhat`` so that the sweep can be replayed alone;
+  * ``mse_*``: ``src.quant_utils.get_quantization_grid`` with ``QuantizationScale.MSE`` (the
+    Triton shrink-factor search, which the reference's own handle never reaches because it
+    compares a string with the Enum) on three small weight matrices stored alongside.
 
 The reference passes ``torch.empty(0, dtype=...)`` to its kernel for the rounding dtype
 (``src/gptq_loop.py:62``); nothing is changed about that.
@@ -127,6 +130,19 @@ def main(ref_root: str, out_dir: str) -> None:
         out[f"{n}.qweight"], out[f"{n}.scale"], out[f"{n}.sweep_codes"] = _np(q), _np(s), _np(codes)
         out[f"{n}.meta"] = np.array(repr(c))
         print(f"{n}: handle vs its own sweep replayed alone {float((q == codes).float().mean()):.5f}")
+
+    import src.quant_utils as ref_qu
+    for k, (R, C, g, dname) in enumerate([(24, 256, 128, "bfloat16"), (16, 256, 32, "float16"), (12, 192, 64, "float32")]):
+        dtype = getattr(torch, dname)
+        W = synthetic.layer_weight(R, C, 2300 + k, dtype)
+        scale, zero, maxq = ref_qu.get_quantization_grid(W.float().to(dev), g, 4, True, dtype, ref_qu.QuantizationScale.MSE)
+        base, _, _ = ref_qu.get_quantization_grid(W.float().to(dev), g, 4, True, dtype, ref_qu.QuantizationScale.ABSMAX)
+        n = f"mse_{dname}_g{g}"
+        out[f"{n}.W"] = _np(W)
+        out[f"{n}.scale"] = _np(scale[:, ::g].contiguous())
+        out[f"{n}.scale_absmax"] = _np(base[:, ::g].contiguous())
+        out[f"{n}.meta"] = np.array(repr(dict(R=R, C=C, g=g, dtype=dname)))
+        print(f"{n}: mean shrink {float((scale / base).mean()):.4f}")
 
     out["environment"] = np.array(repr({"torch": torch.__version__, "device": torch.cuda.get_device_name(0),
                                         "triton": __import__("triton").__version__}))

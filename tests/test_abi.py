@@ -40,7 +40,7 @@ def test_binding_table_matches_header():
 
 def test_abi_version_and_error_text():
     L = _lib.lib()
-    assert L.mq_abi_version() == 1
+    assert L.mq_abi_version() == 2
     # argument validation happens on the host, before any CUDA call
     assert L.mq_pack_int4(None, 4, 8, None, 0, None, None) == 1
     assert b"null pointer" in L.mq_last_error()

@@ -109,6 +109,28 @@ def test_block_loop_matches_oracle_layer_by_layer(cuda, tmp_path, tie):
     cfg = quantization_config(4, 128)
     assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["num_bits"] == 4
 
+    # ---- whole-model writer: shards per block, index and config (pack_quantized_model.py:136-235)
+    import json
+    from moe_quant_b200.writer import pack_model
+    torch.save({"bits": 4, "group_size": 128, "quantize_only_experts": False}, os.path.join(save_dir, "metadata.pt"))
+    packed_dir = str(tmp_path / "packed_model")
+    emb = {"model.embed_tokens.weight": torch.randn(32, 256).to(torch.bfloat16)}
+    tail = {"lm_head.weight": torch.randn(32, 256).to(torch.bfloat16), "model.norm.weight": torch.ones(256).to(torch.bfloat16)}
+    weight_map = pack_model(save_dir, packed_dir, num_blocks=4, block_tensors={3: other}, head_tensors=emb, tail_tensors=tail,
+                            config={"model_type": "deepseek_v3", "hidden_size": 256, "quantization_config": {"stale": True}})
+    with open(os.path.join(packed_dir, "model.safetensors.index.json")) as f:
+        idx = json.load(f)
+    assert idx["metadata"] == {} and idx["weight_map"] == weight_map
+    assert weight_map["model.embed_tokens.weight"] == "model-00001-of-00006.safetensors"
+    assert weight_map["lm_head.weight"] == weight_map["model.norm.weight"] == "model-00006-of-00006.safetensors"
+    assert weight_map[names[0] + ".weight_packed"] == "model-00005-of-00006.safetensors"      # block 3 -> shard 3 + 2
+    shard = load_file(os.path.join(packed_dir, "model-00005-of-00006.safetensors"))
+    assert torch.equal(shard[names[0] + ".weight_packed"], state[names[0] + ".weight_packed"])
+    assert set(os.listdir(packed_dir)) >= {f"model-{i:05}-of-00006.safetensors" for i in range(1, 7)}
+    with open(os.path.join(packed_dir, "config.json")) as f:
+        cfg_file = json.load(f)
+    assert cfg_file["model_type"] == "deepseek_v3" and cfg_file["quantization_config"] == quantization_config(4, 128)
+
 
 def test_routed_expert_regex_matches_reference_names():
     import re

@@ -244,3 +244,62 @@ def test_conv_layer_goes_through_unfold(cuda, precision):
     want = O.quantize_layer(conv.weight.detach().cpu().flatten(1), H, bits=4, group_size=32, rel_damp=1e-2, block_size=128)
     assert torch.equal(s.cpu().float(), want["scale"].float())
     assert O.code_agreement(q.cpu(), want["qweight"]) >= CODE_AGREEMENT
+
+
+def test_mse_scale_search_through_the_handle(cuda):
+    """QuantizationScale.MSE (the Enum member) runs the search; the STRING "mse" gives the
+    absmax grid, as in the reference, whose handle compares a string with the Enum
+    (src/gptq.py:47, src/quant_utils.py:218)."""
+    from moe_quant_b200.quant_utils import QuantizationScale
+    R, C, N = 64, 512, 700
+    W = synthetic.layer_weight(R, C, 71, torch.bfloat16)
+    X = synthetic.activations(N, C, 72, torch.bfloat16)
+    H_raw, _ = O.hessian_update(None, 0, X)
+    want = O.quantize_layer(W, H_raw.clone(), bits=4, group_size=128, block_size=128, mse=True)
+    plain = O.quantize_layer(W, H_raw.clone(), bits=4, group_size=128, block_size=128)
+
+    def run(scale_arg):
+        h = GPTQ(_layer(W, cuda), 128, True, 1e-2, 128, "default", scale_arg)
+        h.update(X.to(cuda))
+        return h.quantize(4)
+
+    q, s, z = run(QuantizationScale.MSE)
+    same = (s.cpu().float() == want["scale"].float())
+    assert float(same.float().mean()) >= 0.97
+    assert float((s.cpu().float() < plain["scale"].float()).float().mean()) > 0.5     # the search shrinks most groups
+    rows_ok = same.all(-1)
+    assert O.code_agreement(q.cpu()[rows_ok], want["qweight"][rows_ok]) >= CODE_AGREEMENT
+    deq = O.dequantize_linear_weight(q.cpu(), s.cpu(), z.cpu()).float()
+    ref = O.dequantize_linear_weight(want["qweight"], want["scale"], want["zero"]).float()
+    e_got, e_ref = O.reconstruction_error(W.float(), deq, H_raw), O.reconstruction_error(W.float(), ref, H_raw)
+    assert abs(e_got - e_ref) <= 0.02 * e_ref
+    q2, s2, _ = run("mse")
+    assert torch.equal(s2.cpu().float(), plain["scale"].float())
+    assert O.code_agreement(q2.cpu(), plain["qweight"]) >= CODE_AGREEMENT
+
+
+@pytest.mark.parametrize("R,C,g,dtype", [(96, 1024, 128, torch.bfloat16), (40, 264, 8, torch.float16), (2048, 2048, 64, torch.bfloat16)])
+def test_quantize_packed_writes_the_words_in_the_sweep(cuda, R, C, g, dtype):
+    """The fused route: same codes and scales as quantize(), and words bit-identical to what the
+    packer (and compressed-tensors' pack_to_int32) makes of those codes."""
+    W = synthetic.layer_weight(R, C, 81, dtype)
+    X = synthetic.activations(600, C, 82, dtype)
+
+    def handle():
+        h = GPTQ(_layer(W, cuda), g, True, 1e-2, 128)
+        h.update(X.to(cuda))
+        return h
+
+    q, s, z = handle().quantize(4)
+    out = handle().quantize_packed(4)
+    assert torch.equal(out["qweight"], q) and torch.equal(out["scale"], s) and torch.equal(out["zero"], z)
+    assert out["weight_packed"].dtype == torch.int32 and out["weight_packed"].shape == (R, C // 8)
+    assert out["weight_shape"].tolist() == [R, C] and out["weight_scale"] is out["scale"]
+    want = O.pack_weight({"qweight": q.cpu(), "scale": s.cpu(), "zero": z.cpu()}, 4, True, g)
+    assert torch.equal(out["weight_packed"].cpu(), want["weight_packed"])
+    # a handle on another route (activation order) packs in a second pass: same contract
+    h = GPTQ(_layer(W, cuda), g, True, 1e-2, 128, "activation")
+    h.update(X.to(cuda))
+    out2 = h.quantize_packed(4)
+    want2 = O.pack_weight({"qweight": out2["qweight"].cpu(), "scale": out2["scale"].cpu(), "zero": out2["zero"].cpu()}, 4, True, g)
+    assert torch.equal(out2["weight_packed"].cpu(), want2["weight_packed"])

@@ -413,3 +413,29 @@ def test_sweep_inverse_free_form_matches_reference_codes(cuda, golden, precision
     assert O.code_agreement(codes.cpu(), golden.t("qweight")) >= 0.999
     want = O.dequantize_linear_weight(codes.cpu(), golden.t("scale", typed=True), golden.t("zero", typed=True))
     assert torch.equal(deq.cpu().float(), want.float())
+
+
+# ------------------------------------------------------------------ MSE scale search
+@pytest.mark.parametrize("R,C,g,dtype", [(64, 512, 128, torch.bfloat16), (40, 256, 32, torch.float16),
+                                         (24, 384, 64, torch.float32), (8, 2048, 2048, torch.bfloat16)])
+def test_mse_scales_match_oracle(cuda, R, C, g, dtype):
+    """The shrink-factor search of src/quant_utils.py:104-139.  The loss sums |.|^2.4 over the
+    group in an order the reference leaves open, so a candidate next to the minimum may win on
+    one side and not the other: nearly all scales must be identical, every scale must be one of
+    the candidates, and its loss must equal the oracle's minimum to rounding."""
+    W = synthetic.layer_weight(R, C, 91, dtype).float()
+    s0, zero, maxq = O.symmetric_grid(W, g, 4, dtype)
+    want = O.mse_scale(W.unflatten(-1, (-1, g)), s0, zero, maxq, dtype)
+    got = ops.mse_scales(W.to(cuda), ops.absmax_scales(W.to(cuda), g, 4, dtype), g, 4, dtype).cpu()
+    assert float((got == want).float().mean()) >= 0.97
+    p = torch.linspace(1, 0.2, 100)
+    cands = O.round_fp(s0[..., None] * p, dtype)
+    assert bool((cands == got[..., None]).any(-1).all())
+
+    def loss(s):
+        Wg = W.unflatten(-1, (-1, g))
+        q = torch.clamp(torch.floor((Wg / s[..., None] + 8.0) + 0.5), 0.0, 15.0)
+        y = O.round_fp((q - 8.0) * s[..., None], dtype)
+        return ((y - Wg).abs().log() * 2.4).exp().sum(-1)
+
+    torch.testing.assert_close(loss(got), loss(want), rtol=1e-3, atol=0)

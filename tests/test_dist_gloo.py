@@ -157,3 +157,46 @@ def test_owner_table_balances_cost_and_keeps_tied_handles_together():
         assert all(0 <= r < world for r in owners)
         assert [r for r in owners].count(owners[4]) == 1 or world == 2, "o_proj dominates: it gets a rank to itself"
     assert len(set(shared_layer_owners(hs, 8))) == 7
+
+
+# ---------------------------------------------------------------------------- expert-parallel block
+def _ep_worker(rank, world, port, out):
+    from moe_quant_b200.synthetic_block import SyntheticMoEBlock
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ep = SyntheticMoEBlock(hidden=64, inter=32, n_experts=8, top_k=2, q_rank=32, kv_rank=32, n_heads=2, nope_dim=16,
+                               rope_dim=16, v_dim=16, seed=5, expert_parallel=True)
+        full = SyntheticMoEBlock(hidden=64, inter=32, n_experts=8, top_k=2, q_rank=32, kv_rank=32, n_heads=2, nope_dim=16,
+                                 rope_dim=16, v_dim=16, seed=5)
+        xs = [torch.randn(2, 24 + 8 * r, 64, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+        local = [i for i, e in enumerate(ep.mlp.experts) if e is not None]
+        assert local == list(range(rank * 4, rank * 4 + 4))
+        seen = {i: 0 for i in local}
+        for i in local:
+            ep.mlp.experts[i].gate_proj.register_forward_hook(
+                lambda _m, inp, _o, i=i: seen.__setitem__(i, seen[i] + inp[0].shape[0]))
+        with torch.no_grad():
+            y_ep = ep(xs[rank])
+            y_full = full(xs[rank])
+            # tokens every rank routes to each expert, from the (identical) router of the full block
+            want = torch.zeros(8, dtype=torch.long)
+            for x in xs:
+                h = x + full.self_attn(full.input_layernorm(x))
+                idx, _ = full.mlp.gate(full.post_attention_layernorm(h).reshape(-1, 64))
+                want += torch.bincount(idx.reshape(-1), minlength=8)
+        ok = torch.allclose(y_ep, y_full, rtol=1e-5, atol=1e-5) and all(seen[i] == int(want[i]) for i in local)
+        flag = torch.tensor([float(ok)])
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            torch.save({"ok": bool(flag.item()), "seen": seen, "want": want.tolist()}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_block_routes_tokens_to_the_owning_rank(tmp_path):
+    out = str(tmp_path / "ep.pt")
+    mp.spawn(_ep_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["ok"], res

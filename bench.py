@@ -229,6 +229,7 @@ def run_b200(args):
     cx.clocks = ClockSampler(local)         # NVML comes up here, not beside the timed region
     cx.peaks = _peaks()
     cx.seed = 1234 + 100 * rank
+    cx.no_cpu_baseline = args.no_cpu_baseline
     n_experts = 4
 
     def barrier():
@@ -280,7 +281,12 @@ def run_b200(args):
     if want in ("all", "down_proj") and rank == 0:
         extra["down_proj"] = _guarded(wl_down_proj, cx)
     if want in ("all", "moe_layer"):
-        extra["moe_layer"] = _guarded(wl_moe_layer, cx)
+        res = _guarded(wl_moe_layer, cx)        # no collective inside: a failure on one rank cannot hang the others
+        total = cx.max_over_ranks(float(res.get("layer_ms_local", 0.0)))
+        if "error" not in res and total > 0:
+            res["layer_ms_max_over_ranks"] = total
+            res["layers_per_s_all_ranks"] = world * res["layers_per_rank"] / (total / 1e3)
+        extra["moe_layer"] = res
     if want in ("all", "mla"):
         extra["mla"] = wl_mla(cx)                 # collectives inside: every rank must take part, no guard
     cx.clocks.close()
@@ -585,23 +591,37 @@ def cx_no_cpu(cx):
 
 def parity_sample(cx):
     """Untimed: one of the benchmark's own experts (its ragged token count) quantized once, the
-    first 64 rows compared with the CPU oracle fed with the same Hessian."""
-    from moe_quant_b200 import GPTQ
+    first 128 rows compared with the CPU oracle fed with the same Hessian.  Beside the engine's
+    figure stands the oracle's own noise floor on this Hessian: its fp32 route against the same
+    route with the factor computed in fp64.  (With far fewer tokens than input channels the
+    damped Hessian is so ill conditioned that a code on a rounding boundary flips with the last
+    bits of the factor, and one flip changes a third of the codes behind it in that row.)"""
     from oracle import gptq_oracle as O
 
-    rows = 64
+    rows = 128
     h = cx.make_handles(1)[0]
     H_raw = h.H.clone()
     q, s, z = h.quantize(BITS)
     Wc = cx.weights[0][:rows].cpu()
-    want = O.quantize_layer(Wc, H_raw.cpu(), bits=BITS, group_size=GROUP, rel_damp=1e-2, block_size=128)
+    Hc = H_raw.cpu()
+    want = O.quantize_layer(Wc, Hc.clone(), bits=BITS, group_size=GROUP, rel_damp=1e-2, block_size=128)
     got = O.dequantize_linear_weight(q[:rows].cpu(), s[:rows].cpu(), z[:rows].cpu()).float()
     ref = O.dequantize_linear_weight(want["qweight"], want["scale"], want["zero"]).float()
-    Hc = cx.hessians[0].cpu()
-    return {"rows": rows, "tokens": cx.tokens[0], "code_agreement": O.code_agreement(q[:rows].cpu(), want["qweight"]),
-            "scales_equal": bool(torch.equal(s[:rows].cpu().float(), want["scale"].float())),
-            "recon_error": O.reconstruction_error(Wc.float(), got, Hc),
-            "recon_error_oracle": O.reconstruction_error(Wc.float(), ref, Hc)}
+    out = {"rows": rows, "tokens": cx.tokens[0], "code_agreement": O.code_agreement(q[:rows].cpu(), want["qweight"]),
+           "scales_equal": bool(torch.equal(s[:rows].cpu().float(), want["scale"].float())),
+           "recon_error": O.reconstruction_error(Wc.float(), got, Hc),
+           "recon_error_oracle": O.reconstruction_error(Wc.float(), ref, Hc)}
+    if not cx_no_cpu(cx):
+        Hp, Wf, _, _ = O.pre_step(Hc.clone(), Wc)
+        Hd = Hp.double()
+        Hd += 1e-2 * torch.diag(Hd).mean() * torch.eye(Hd.shape[0], dtype=torch.float64)
+        U = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hd)), upper=True)
+        U = (U / U.diag()[:, None]).float().contiguous()
+        sc, zr, maxq = O.symmetric_grid(Wf, GROUP, BITS, Wc.dtype)
+        Q = O.gptq_sweep(Wf.t().contiguous(), U, sc.repeat_interleave(GROUP, -1).t().contiguous(),
+                         zr.repeat_interleave(GROUP, -1).t().contiguous(), maxq, Wc.dtype, 128)
+        out["oracle_fp32_vs_fp64_factor"] = O.code_agreement(Q.t().contiguous().to(torch.uint8), want["qweight"])
+    return out
 
 
 # ---------------------------------------------------------------------------- the other named workloads
@@ -686,7 +706,7 @@ def wl_moe_layer(cx):
         gates = [GPTQ(_linear(w), GROUP, True, 1e-2, 128) for w in Wg]
         ups = [GPTQ(_linear(w), GROUP, True, 1e-2, 128, tied_gptq_handle=g) for w, g in zip(Wu, gates)]
         downs = [GPTQ(_linear(w), GROUP, True, 1e-2, 128) for w in Wd]
-        cx.barrier()
+        torch.cuda.synchronize()
         e0, e1, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for e in range(n_exp):                       # the Hessian pass: what the forward hooks do
@@ -704,7 +724,7 @@ def wl_moe_layer(cx):
             cur.wait_stream(st)
         res.append(quantize_many(downs, BITS, streams=cx.n_streams))
         e2.record()
-        cx.barrier()
+        torch.cuda.synchronize()
         issues = sum(h.has_hessian_issues() for h in gates + ups + downs)
         return e0.elapsed_time(e1), e1.elapsed_time(e2), issues
 
@@ -712,11 +732,11 @@ def wl_moe_layer(cx):
     runs = [one_pass() for _ in range(2)]
     h_ms = statistics.median(r[0] for r in runs)
     q_ms = statistics.median(r[1] for r in runs)
-    total = cx.max_over_ranks(h_ms + q_ms)
+    total = h_ms + q_ms
     flop_h = sum(m * hidden * (hidden + 1) + m * inter * (inter + 1) for m in mine)
     return {"experts_per_rank": n_exp, "layers_per_rank": 3 * n_exp, "tokens_per_expert_min_mean_max":
             [min(mine), sum(mine) / n_exp, max(mine)], "hessian_pass_ms": h_ms, "quantize_ms": q_ms,
-            "layer_ms_max_over_ranks": total, "layers_per_s_all_ranks": cx.world * 3 * n_exp / (total / 1e3),
+            "layer_ms_local": total,
             "hessian_tflops_unique": flop_h / (h_ms / 1e3) / 1e12, "hessian_issues": int(runs[-1][2])}
 
 

@@ -31,42 +31,26 @@ constexpr int NB = 128;  // panel width
 
 // ------------------------------------------------------------------ diagonal block
 // D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
-// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers.  The 128 pivots are
-// taken 8 at a time, tile column 15 first.  The sixteen threads of tile column kt form one
-// half-warp (columns w and w + 8 live in warp w).  When its turn comes the half-warp works alone:
-// the owner of the diagonal tile publishes it, every lane factors its own copy in registers
-// (the same arithmetic 16 times, no communication inside the chain of 8 pivots) and applies each
-// pivot to its 8 rows of the panel above the leaf as soon as it exists, so the panel solve
-// fills the latency gaps of the pivot chain; the panel (8 columns of T above the leaf) goes to
-// shared memory and a ready flag is raised.
-//
-// There is no block-wide barrier.  Every tile column has its own panel buffer and its own flag;
-// a thread applies the rank-8 update of panel kt to its tile as soon as flag kt is up, in the
-// order kt = 15, 14, ..., and a half-warp factors its leaf right after the last update its column
-// needs.  The serial path of a step is therefore one rank-8 update of one tile column, the
-// pivot chain and the flag, instead of a barrier round over the whole block; updates of the
-// other tile columns run in the shadow of later leaves.  A warp never waits for itself: its
-// upper column is factored inside its own instruction stream before its lower column needs it.
-// The waits are bounded; one that expires marks the block as not positive (the factor is then
-// replaced by the identity downstream) instead of hanging.
+// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers, and the 16 threads
+// of one tile column are the 16 lanes of a half-warp.  The 128 pivots are taken 8 at a time.
+// For leaf kt the half-warp of tile column kt works alone: the owner of the diagonal tile
+// publishes it, every lane factors its own copy in registers (the same arithmetic 16 times,
+// no communication inside the chain of 8 pivots) and applies each pivot to its 8 rows of the
+// panel above the leaf as soon as it exists, so the panel solve fills the latency gaps of the
+// pivot chain.  One block-wide barrier per leaf; then every remaining upper tile takes one
+// rank-8 update from the panel, which is double buffered so that the next leaf's half-warp
+// may write its panel while slower warps still read this one.
 constexpr int PAN_LD = NB + 4;
-constexpr size_t kDiagSmem = (size_t)(16 * 8 * PAN_LD + 16 * 64) * sizeof(float);
 
 __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                             int k_global, mq_layer_flags* flags) {
-  extern __shared__ __align__(16) float diag_smem[];
-  float (*pan)[8][PAN_LD] = reinterpret_cast<float (*)[8][PAN_LD]>(diag_smem);       // pan[kt][kk][row]: column 8kt+kk of T above leaf kt
-  float (*leaf_pub)[8][8] = reinterpret_cast<float (*)[8][8]>(diag_smem + 16 * 8 * PAN_LD);  // diagonal tile kt before its factorisation
-  __shared__ int ready[16];
-  const int t = threadIdx.x;
-  if (t < 16) ready[t] = 0;
-  __syncthreads();
+  __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of T, rows above the leaf
+  __shared__ __align__(16) float leaf_pub[8][8];     // the diagonal tile before its factorisation
   chain_wait();
   chain_release();
+  const int t = threadIdx.x;
   const int warp = t >> 5, lane = t & 31;
-  const int half = lane >> 4, tr = lane & 15;
-  const int tc = warp + 8 * half;
-  const unsigned half_mask = half ? 0xFFFF0000u : 0x0000FFFFu;
+  const int tc = warp * 2 + (lane >> 4), tr = lane & 15;
   float a[8][8];
   // Only tiles on or above the diagonal are ever read.  A whole, 16-byte aligned block moves
   // as float4 (a quarter of the memory transactions of scalar accesses at this tile layout).
@@ -90,98 +74,81 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
         a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
       }
   }
-  for (int kt = 15; kt >= warp; --kt) {
-    if (kt == warp + 8 || kt == warp) {
-      // ---- this warp owns tile column kt: the half-warp that holds it factors the leaf
-      if (tc == kt) {
-        if (tr == kt) {
+  for (int kt = 15; kt >= 0; --kt) {
+    const int buf = kt & 1;
+    if (warp == (kt >> 1)) {
+      if (tc == kt && tr == kt) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            *reinterpret_cast<float4*>(&leaf_pub[kt][i][0]) = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
-            *reinterpret_cast<float4*>(&leaf_pub[kt][i][4]) = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
-          }
+        for (int i = 0; i < 8; ++i) {
+          *reinterpret_cast<float4*>(&leaf_pub[i][0]) = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
+          *reinterpret_cast<float4*>(&leaf_pub[i][4]) = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
         }
-        __syncwarp(half_mask);
-        if (tr <= kt) {
-          float L[8][8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 lo = *reinterpret_cast<const float4*>(&leaf_pub[kt][i][0]);
-            const float4 hi = *reinterpret_cast<const float4*>(&leaf_pub[kt][i][4]);
-            L[i][0] = lo.x; L[i][1] = lo.y; L[i][2] = lo.z; L[i][3] = lo.w;
-            L[i][4] = hi.x; L[i][5] = hi.y; L[i][6] = hi.z; L[i][7] = hi.w;
-          }
-          // The 8 pivots are one straight line of code (no branch), so that the scheduler can
-          // put the panel arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.
-          // The owner of the diagonal tile runs the panel arithmetic on its own tile too; that
-          // copy is discarded below.
-          int fail = 0;
-#pragma unroll
-          for (int kk = 7; kk >= 0; --kk) {
-            float d = L[kk][kk];
-            const bool bad = !(d > 0.0f);  // also catches NaN
-            fail = (bad && fail == 0) ? kk + 1 : fail;
-            d = bad ? 1.0f : d;
-            float r = rsqrtf(d);
-            r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
-            L[kk][kk] = d * r;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (i < kk) L[i][kk] *= r;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (i <= j && j < kk) L[i][j] = fmaf(-L[i][kk], L[j][kk], L[i][j]);
-            // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float pv = a[i][kk] * r;
-              a[i][kk] = pv;
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (j < kk) a[i][j] = fmaf(-pv, L[j][kk], a[i][j]);
-            }
-          }
-          if (tr < kt) {
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-              *reinterpret_cast<float4*>(&pan[kt][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-              *reinterpret_cast<float4*>(&pan[kt][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
-            }
-          } else {
-            if (fail != 0 && kt * 8 + fail - 1 < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + fail);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) a[i][j] = (i <= j) ? L[i][j] : 0.0f;
-          }
-        }
-        __syncwarp(half_mask);
-        __threadfence_block();
-        if (tr == 0) *reinterpret_cast<volatile int*>(&ready[kt]) = 1;
       }
       __syncwarp();
-      if (kt == warp) break;  // the warp's lower column is done: nothing left for this warp
-    } else {
-      // ---- another warp owns tile column kt: wait for its panel (bounded)
-      const long long t0 = clock64();
-      while (*reinterpret_cast<volatile int*>(&ready[kt]) == 0) {
-        if (clock64() - t0 > 200000000ll) {  // about 0.1 s: give up, mark the block as failed
-          atomicCAS(&flags->not_positive, 0, k_global + 1);
-          break;
+      if (tc == kt && tr <= kt) {
+        float L[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 lo = *reinterpret_cast<const float4*>(&leaf_pub[i][0]);
+          const float4 hi = *reinterpret_cast<const float4*>(&leaf_pub[i][4]);
+          L[i][0] = lo.x; L[i][1] = lo.y; L[i][2] = lo.z; L[i][3] = lo.w;
+          L[i][4] = hi.x; L[i][5] = hi.y; L[i][6] = hi.z; L[i][7] = hi.w;
+        }
+        // The 8 pivots are one straight line of code (no branch), so that the scheduler can
+        // put the panel arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.
+        // The owner of the diagonal tile runs the panel arithmetic on its own tile too; that
+        // copy is discarded below.
+        int fail = 0;
+#pragma unroll
+        for (int kk = 7; kk >= 0; --kk) {
+          float d = L[kk][kk];
+          const bool bad = !(d > 0.0f);  // also catches NaN
+          fail = (bad && fail == 0) ? kk + 1 : fail;
+          d = bad ? 1.0f : d;
+          float r = rsqrtf(d);
+          r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
+          L[kk][kk] = d * r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < kk) L[i][kk] *= r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i <= j && j < kk) L[i][j] = fmaf(-L[i][kk], L[j][kk], L[i][j]);
+          // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float pv = a[i][kk] * r;
+            a[i][kk] = pv;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j < kk) a[i][j] = fmaf(-pv, L[j][kk], a[i][j]);
+          }
+        }
+        if (tr < kt) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
+            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
+          }
+        } else {
+          if (fail != 0 && kt * 8 + fail - 1 < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + fail);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[i][j] = (i <= j) ? L[i][j] : 0.0f;
         }
       }
     }
-    __threadfence_block();
-    // ---- rank-8 update of this thread's tile from panel kt
+    __syncthreads();
     if (tr <= tc && tc < kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const float4 i0 = *reinterpret_cast<const float4*>(&pan[kt][kk][tr * 8]);
-        const float4 i1 = *reinterpret_cast<const float4*>(&pan[kt][kk][tr * 8 + 4]);
-        const float4 j0 = *reinterpret_cast<const float4*>(&pan[kt][kk][tc * 8]);
-        const float4 j1 = *reinterpret_cast<const float4*>(&pan[kt][kk][tc * 8 + 4]);
+        const float4 i0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8]);
+        const float4 i1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8 + 4]);
+        const float4 j0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8]);
+        const float4 j1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8 + 4]);
         const float pi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
         const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
         // two columns per instruction (packed fp32 FMA: each half is an ordinary fma.rn)
@@ -458,7 +425,6 @@ int configure_once() {
   if (!done[dev & 63]) {
     MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
     MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
-    MQ_CUDA(cudaFuncSetAttribute(chol_diag_rev_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDiagSmem));
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -486,43 +452,45 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   // Tensor path: the panel solve writes its result as bf16 planes too, and the rank-128 update
   // P P^T reads one plane set as both operands.
   const bool tensor = math == MQ_MATH_TENSOR;
-  PlaneSet pset;
-  if (tensor) {
-    MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "factorisation: split must be 1, 2 or 3 (got %d)", split);
-    Workspace mine = eng.ws;
-    pset.base = mine.take<uint16_t>(plane_set_bytes(C, NB, split) / 2);
-    MQ_REQUIRE(pset.base, MQ_ERR_WORKSPACE, "factorisation: workspace too small for the panel planes");
-    pset.planes = split; pset.rows_pad = (int)pad_rows(C); pset.total_rows = pset.rows_pad; pset.K_pad = NB;
-  }
-  // ---- factorisation, last panel first
-  for (int p = P - 1; p >= 0; --p) {
-    const int64_t k1 = (int64_t)p * NB;
-    const int nb = (int)((C - k1) < NB ? (C - k1) : NB);
-    float* dblk = H + k1 * ldh + k1;
-    {
-      ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
-      MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(256), kDiagSmem, st, dblk, ldh, nb, (int)k1, flags));
-    }
-    MQ_LAUNCH_CHECK();
-    if (k1 == 0) break;
-    int grid = (int)(ceil_div(k1, 32) < 148 * 2 ? ceil_div(k1, 32) : 148 * 2);
-    {
-      ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
-      MQ_CUDA(launch_chained(true, trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
-                             (int)k1, nb, 0, tensor ? pset.base : nullptr, tensor ? pset.total_rows * NB : 0, split));
-    }
-    MQ_LAUNCH_CHECK();
-    GemmDesc g;
-    g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;
-    g.B = H + k1; g.b_rs = 1; g.b_cs = ldh;
-    g.C = H; g.ldc = ldh;
-    g.M = (int)k1; g.N = (int)k1; g.K = nb;
-    g.alpha = -1.0f; g.beta = 1.0f;
-    g.upper_tiles_only = 1;
+  if (tensor) MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "factorisation: split must be 1, 2 or 3 (got %d)", split);
+  {
+    // ---- right-looking loop, last panel first
+    PlaneSet pset;
     if (tensor) {
-      MQ_TRY(gemm_tensor_planes(g, pset, pset, st));
-    } else {
-      MQ_TRY(eng.gemm(g));
+      Workspace mine = eng.ws;
+      pset.base = mine.take<uint16_t>(plane_set_bytes(C, NB, split) / 2);
+      MQ_REQUIRE(pset.base, MQ_ERR_WORKSPACE, "factorisation: workspace too small for the panel planes");
+      pset.planes = split; pset.rows_pad = (int)pad_rows(C); pset.total_rows = pset.rows_pad; pset.K_pad = NB;
+    }
+    for (int p = P - 1; p >= 0; --p) {
+      const int64_t k1 = (int64_t)p * NB;
+      const int nb = (int)((C - k1) < NB ? (C - k1) : NB);
+      float* dblk = H + k1 * ldh + k1;
+      {
+        ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
+        MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(256), 0, st, dblk, ldh, nb, (int)k1, flags));
+      }
+      MQ_LAUNCH_CHECK();
+      if (k1 == 0) break;
+      const int grid = (int)(ceil_div(k1, 32) < 148 * 2 ? ceil_div(k1, 32) : 148 * 2);
+      {
+        ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
+        MQ_CUDA(launch_chained(true, trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
+                               (int)k1, nb, 0, tensor ? pset.base : nullptr, tensor ? pset.total_rows * NB : 0, split));
+      }
+      MQ_LAUNCH_CHECK();
+      GemmDesc g;
+      g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;
+      g.B = H + k1; g.b_rs = 1; g.b_cs = ldh;
+      g.C = H; g.ldc = ldh;
+      g.M = (int)k1; g.N = (int)k1; g.K = nb;
+      g.alpha = -1.0f; g.beta = 1.0f;
+      g.upper_tiles_only = 1;
+      if (tensor) {
+        MQ_TRY(gemm_tensor_planes(g, pset, pset, st));
+      } else {
+        MQ_TRY(eng.gemm(g));
+      }
     }
   }
   // ---- T -> unit-diagonal factor

@@ -21,16 +21,25 @@ __device__ __forceinline__ uint32_t pack8(uint32_t lo4, uint32_t hi4) {
 }
 
 // Fast path: symmetric (zero == 8, nibble == code), C % 16 == 0, 16-byte aligned base.
-// One thread turns 16 codes into two words.
+// One thread turns 16 codes into two words, four such vectors per trip with all four loads
+// issued before the first is used: a 22 MB matrix is one short wave of CTAs, so what counts is
+// how many bytes every thread has in flight, not how many trips it makes.
+constexpr int kPackUnroll = 4;
 __global__ void __launch_bounds__(kPackThreads) pack_int4_vec16(const uint4* __restrict__ codes,
                                                                 uint2* __restrict__ packed, int64_t n_vec) {
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    uint4 c = __ldg(codes + i);
-    uint2 w;
-    w.x = pack8(c.x, c.y);
-    w.y = pack8(c.z, c.w);
-    packed[i] = w;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n_vec; i0 += stride * kPackUnroll) {
+    uint4 c[kPackUnroll];
+#pragma unroll
+    for (int u = 0; u < kPackUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      c[u] = i < n_vec ? __ldcs(codes + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < kPackUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < n_vec) __stcs(packed + i, make_uint2(pack8(c[u].x, c[u].y), pack8(c[u].z, c[u].w)));
+    }
   }
 }
 
@@ -110,7 +119,7 @@ extern "C" int mq_pack_int4(const uint8_t* codes, int64_t R, int64_t C, const in
   ProfScope prof(PROF_PACK, 1.5 * (double)R * (double)C, 0.0, st);
   if (!zero_i8 && C % 16 == 0 && aligned(codes, 16) && aligned(packed, 8)) {
     int64_t n_vec = R * C / 16;
-    pack_int4_vec16<<<grid_for(n_vec, kPackThreads), kPackThreads, 0, st>>>(
+    pack_int4_vec16<<<grid_for(ceil_div(n_vec, kPackUnroll), kPackThreads), kPackThreads, 0, st>>>(
         reinterpret_cast<const uint4*>(codes), reinterpret_cast<uint2*>(packed), n_vec);
   } else {
     int64_t n = R * ((C + 7) / 8);

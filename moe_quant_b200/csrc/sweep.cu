@@ -17,8 +17,6 @@
 //   W[:, later] += E Uhat[tile, later]             (src/gptq_loop.py:148)
 // is a GEMM through the Engine.  Codes are written straight into the (R, C) uint8
 // result, so the transposes of src/gptq.py:191-199 never happen.
-#include <stdlib.h>
-
 #include "engine.cuh"
 #include "profile.cuh"
 
@@ -36,23 +34,12 @@ constexpr int ROWS_PER_CTA = SWEEP_THREADS / ROW_LANES;  // 16
 constexpr int U_LANE_LD = LANE_COLS + 4;
 constexpr int U_ROW_LD = ROW_LANES * U_LANE_LD;          // 160 floats
 constexpr size_t kSweepSmem = (size_t)TILE * U_ROW_LD * sizeof(float);
-// A launch sweeps a super-block of up to SUPER_TILES tiles (512 columns).  Inside it a tile's
-// errors reach the later tiles of the super-block as fp32 FMAs in the kernel itself; only the
-// columns behind the super-block are updated by a GEMM, with all 512 errors of a row at once.
-constexpr int SUPER_TILES = 4;
-constexpr int SUPER = SUPER_TILES * TILE;
-
-// eight codes below 16, held as bytes in two words (lowest byte = first column) -> one word of nibbles
-__device__ __forceinline__ uint32_t pack_nibbles(uint32_t lo4, uint32_t hi4) {
-  const uint32_t w = (lo4 & 0xFu) | ((lo4 >> 4) & 0xF0u) | ((lo4 >> 8) & 0xF00u) | ((lo4 >> 12) & 0xF000u);
-  const uint32_t v = (hi4 & 0xFu) | ((hi4 >> 4) & 0xF0u) | ((hi4 >> 8) & 0xF00u) | ((hi4 >> 12) & 0xF000u);
-  return w | (v << 16);
-}
 
 // One 128 x 128 tile of the factor (top-left element at `src`) -> shared memory in the chunked
-// row layout, strict upper triangle only.  stage: issue the copies; trim: wait for them and zero
-// the entries on and below the diagonal inside each row's diagonal quad.  Every thread of the
-// CTA must call both.
+// row layout, strict upper triangle only.  stage: issue the copies (asynchronous 16-byte copies,
+// all in flight at once; a copy with source size 0 writes zeros: everything below the diagonal
+// and past nb); trim: wait for them and zero the entries on and below the diagonal inside each
+// row's diagonal quad.  Every thread of the CTA must call both.
 __device__ __forceinline__ void stage_factor_tile(float* ublk, const float* __restrict__ src, int64_t ldu, int nb) {
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += SWEEP_THREADS) {
     const int j = idx >> 5, k4 = (idx & 31) * 4;
@@ -75,6 +62,13 @@ __device__ __forceinline__ void trim_factor_tile(float* ublk, int nb) {
   __syncthreads();
 }
 
+// eight codes below 16, held as bytes in two words (lowest byte = first column) -> one word of nibbles
+__device__ __forceinline__ uint32_t pack_nibbles(uint32_t lo4, uint32_t hi4) {
+  const uint32_t w = (lo4 & 0xFu) | ((lo4 >> 4) & 0xF0u) | ((lo4 >> 8) & 0xF00u) | ((lo4 >> 12) & 0xF000u);
+  const uint32_t v = (hi4 & 0xFu) | ((hi4 >> 4) & 0xF0u) | ((hi4 >> 8) & 0xF00u) | ((hi4 >> 12) & 0xF000u);
+  return w | (v << 16);
+}
+
 struct SweepArgs {
   const float* W; int64_t ldw; int R;
   const float* U; int64_t ldu;
@@ -82,12 +76,11 @@ struct SweepArgs {
   float maxq, zero_default;
   uint8_t* codes; int64_t C;
   int32_t* packed;   // optional (R, C/8) int32: the same codes, eight 4-bit nibbles per word
-  void* deq;
-  float* err;        // (R, SUPER) fp32: the errors of the super-block, column k at [r * SUPER + k]
-  int i1, nb;        // first column and width of the super-block
+  void* deq; float* err;
+  int i1, nb;
   const float* Worig; int64_t ldwo;
-  uint16_t* err_planes; int64_t plane_stride; int n_planes;   // the same errors as bf16 planes, (R_pad, SUPER) per plane
-  const float* col_div;   // optional: above its diagonal tiles U holds the factor before column c was divided by col_div[c]
+  uint16_t* err_planes; int64_t plane_stride; int n_planes;
+  int bits;
 };
 
 // UNIFORM: the sixteen columns of a lane lie in one quantization group (group % 16 == 0).
@@ -95,37 +88,25 @@ template <int DT, bool UNIFORM>
 __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepArgs a) {
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][U_ROW_LD], strict upper triangle of the tile, 0 elsewhere
-  const int sb0 = a.i1, sbw = a.nb;
-  const int n_tiles = (sbw + TILE - 1) / TILE;
-  // The factor is constant during the sweep: its first tile is staged before this grid waits for
-  // the update that precedes it in the stream (only W depends on that update).  The quads go
-  // from global to shared memory as asynchronous 16-byte copies, all in flight at once (a copy
-  // with source size 0 writes zeros: everything below the diagonal and past the tile's width);
-  // the quad that straddles the diagonal of each row is trimmed afterwards.
-  stage_factor_tile(ublk, a.U + (int64_t)sb0 * a.ldu + sb0, a.ldu, sbw < TILE ? sbw : TILE);
+  const int nb = a.nb, i1 = a.i1;
+  // The factor is constant during the sweep: its tile is staged before this grid waits for the
+  // rank-128 update that precedes it in the stream (only W depends on that update).
+  stage_factor_tile(ublk, a.U + (int64_t)i1 * a.ldu + i1, a.ldu, nb);
   chain_wait();
   chain_release();
+  trim_factor_tile(ublk, nb);
 
   const int sub = threadIdx.x & (ROW_LANES - 1);   // this lane's chunk of the row
   const int c_local = sub * LANE_COLS;
+  const int c0 = i1 + c_local;
   const float maxq = a.maxq;
   // Inverse-free form (Worig != nullptr): U is the unit factor Utilde = Uhat^-1 and what is
   // propagated is minus the total change of the column, -(y - w_original), instead of the
   // error against the running value; x_j = w_j - sum_{i<j} (y_i - w_i) Utilde[i,j] is the same
   // number as the reference's running weight (E Uhat = Y - W  <=>  E = (Y - W) Utilde).
   const bool inverse_free = a.Worig != nullptr;
-  const int row_groups = (a.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-
-  for (int tile = 0; tile < n_tiles; ++tile) {
-  const int i1 = sb0 + tile * TILE;
-  const int nb = (sbw - tile * TILE) < TILE ? (sbw - tile * TILE) : TILE;
-  if (tile > 0) {
-    __syncthreads();   // every warp is done with the previous tile of the factor
-    stage_factor_tile(ublk, a.U + (int64_t)i1 * a.ldu + i1, a.ldu, nb);
-  }
-  trim_factor_tile(ublk, nb);
-  const int c0 = i1 + c_local;
   const int n_owner = (nb + LANE_COLS - 1) / LANE_COLS;
+  const int row_groups = (a.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
 
   // the CTA walks row groups together (the shuffles below are warp-wide); rows past R carry zeros
   for (int rg = blockIdx.x; rg < row_groups; rg += gridDim.x) {
@@ -141,44 +122,6 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
       }
       w[4 * qd] = v.x; w[4 * qd + 1] = v.y; w[4 * qd + 2] = v.z; w[4 * qd + 3] = v.w;
       wo[4 * qd] = vo.x; wo[4 * qd + 1] = vo.y; wo[4 * qd + 2] = vo.z; wo[4 * qd + 3] = vo.w;
-    }
-    if (tile > 0) {
-      // What the earlier tiles of this super-block owe these columns (the lazy update of
-      // src/gptq_loop.py:148 for the part of it that stays inside the super-block):
-      //   w_k += sum_i e_i U[i, k]   over the columns i of tiles 0 .. tile-1,
-      // fp32 FMAs in increasing i, one sum per column added to the weight at the end.  The
-      // errors come from the fp32 scratch the earlier tiles wrote (this CTA wrote these rows
-      // itself, before the barrier above), the rows of the factor straight from global memory:
-      // the four rows of a warp and the four warps of the CTA read the same addresses.
-      float acc[LANE_COLS];
-#pragma unroll
-      for (int k = 0; k < LANE_COLS; ++k) acc[k] = 0.0f;
-      const float* er = a.err + (int64_t)(valid ? r : 0) * SUPER;
-      const float* ub = a.U + (int64_t)sb0 * a.ldu + c0;
-      const int n_prev = tile * TILE;
-#pragma unroll 2
-      for (int i4 = 0; i4 < n_prev; i4 += 4) {
-        const float4 e4 = valid ? *reinterpret_cast<const float4*>(er + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const float ev[4] = {e4.x, e4.y, e4.z, e4.w};
-#pragma unroll
-        for (int ii = 0; ii < 4; ++ii) {
-          const float2 e2 = make_float2(ev[ii], ev[ii]);
-          const float* urow = ub + (int64_t)(i4 + ii) * a.ldu;
-#pragma unroll
-          for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
-            if (c_local + 4 * qd >= nb) continue;
-            const float4 u = __ldg(reinterpret_cast<const float4*>(urow + 4 * qd));
-            const float2 p01 = __ffma2_rn(make_float2(u.x, u.y), e2, make_float2(acc[4 * qd], acc[4 * qd + 1]));
-            const float2 p23 = __ffma2_rn(make_float2(u.z, u.w), e2, make_float2(acc[4 * qd + 2], acc[4 * qd + 3]));
-            acc[4 * qd] = p01.x; acc[4 * qd + 1] = p01.y; acc[4 * qd + 2] = p23.x; acc[4 * qd + 3] = p23.y;
-          }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < LANE_COLS; ++k) {
-        if (a.col_div && c_local + k < nb) acc[k] = acc[k] / __ldg(a.col_div + c0 + k);
-        w[k] += acc[k];
-      }
     }
     // grid of the lane's columns; x / s goes through the reciprocal and one correction step (the
     // final stage of a correctly rounded division): a few FMAs on the serial chain instead of
@@ -196,81 +139,44 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
       }
       rs[t] = 1.0f / sc[t];
     }
+    // what this lane produces when its turn comes: the errors of its sixteen columns and their
+    // codes, two to a float (q0 + 256 q1 is exact for codes below 256)
+    float e[LANE_COLS], qacc[LANE_COLS / 2];
+#pragma unroll
+    for (int t = 0; t < LANE_COLS; ++t) e[t] = 0.0f;
+#pragma unroll
+    for (int h = 0; h < LANE_COLS / 2; ++h) qacc[h] = 0.0f;
 
 #pragma unroll 1
     for (int lo = 0; lo < n_owner; ++lo) {
-      // Chain of the sixteen columns that lane `lo` of every row owns.  Every lane runs the same
-      // sixteen steps on a copy of its own values against that lane's diagonal 16 x 16 block
-      // (uniform code, one shared-memory address per load for the whole warp); only lane lo's
-      // results are real.
-      const float* ud = &ublk[(lo * LANE_COLS) * U_ROW_LD + lo * U_LANE_LD];
-      float wl[LANE_COLS], e[LANE_COLS];
-      uint32_t qp[LANE_COLS / 4] = {0u, 0u, 0u, 0u};
+      if (sub == lo) {
+        // Chain of this lane's sixteen columns against its diagonal 16 x 16 block of the factor
+        // (the four lanes of the warp that own chunk `lo` of their rows run it; the others wait).
+        // A step applies the error to the whole quad rows behind it: entries on and below the
+        // diagonal are zero in the staged tile and the columns they touch are finished.
+        const float* ud = &ublk[(lo * LANE_COLS) * U_ROW_LD + lo * U_LANE_LD];
 #pragma unroll
-      for (int t = 0; t < LANE_COLS; ++t) wl[t] = w[t];
+        for (int t = 0; t < LANE_COLS; ++t) {
+          const float s_t = sc[UNIFORM ? 0 : t], z_t = zr[UNIFORM ? 0 : t], r_t = rs[UNIFORM ? 0 : t];
+          const float x = w[t];
+          float d = x * r_t;
+          d = fmaf(fmaf(-s_t, d, x), r_t, d);
+          const float q = fminf(fmaxf(floorf((d + z_t) + 0.5f), 0.0f), maxq);
+          const float y = round_through<DT>((q - z_t) * s_t);
+          const float et = inverse_free ? (wo[t] - y) : (y - x);
+          e[t] = et;
+          qacc[t >> 1] = (t & 1) ? fmaf(q, 256.0f, qacc[t >> 1]) : q;
+          const float2 e2 = make_float2(et, et);
 #pragma unroll
-      for (int t = 0; t < LANE_COLS; ++t) {
-        const float s_t = sc[UNIFORM ? 0 : t], z_t = zr[UNIFORM ? 0 : t], r_t = rs[UNIFORM ? 0 : t];
-        const float x = wl[t];
-        float d = x * r_t;
-        d = fmaf(fmaf(-s_t, d, x), r_t, d);
-        const float q = fminf(fmaxf(floorf((d + z_t) + 0.5f), 0.0f), maxq);
-        const float y = round_through<DT>((q - z_t) * s_t);
-        const float et = inverse_free ? (wo[t] - y) : (y - x);
-        e[t] = et;
-        qp[t >> 2] |= (uint32_t)q << (8 * (t & 3));
-#pragma unroll
-        for (int t2 = t + 1; t2 < LANE_COLS; ++t2) wl[t2] = fmaf(ud[t * U_ROW_LD + t2], et, wl[t2]);
-      }
-      if (sub == lo && valid) {
-        // this lane's sixteen columns are final: codes, optional dequantized values, errors
-#pragma unroll
-        for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
-          if (c_local + 4 * qd >= nb) continue;
-          *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.C + c0 + 4 * qd) = qp[qd];
-          // the compressed-tensors word of columns 8k..8k+7 (column 8k+i at bits 4i..4i+3), written
-          // here so that no separate packing pass has to read the codes back
-          if (a.packed && (qd & 1)) a.packed[(int64_t)r * (a.C >> 3) + ((c0 + 4 * qd) >> 3)] = (int32_t)pack_nibbles(qp[qd - 1], qp[qd]);
-          if (a.deq) {
-            T* dq = static_cast<T*>(a.deq) + (int64_t)r * a.C + c0 + 4 * qd;
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float qf = (float)((qp[qd] >> (8 * t)) & 0xFFu);
-              dq[t] = from_float<T>((qf - zr[UNIFORM ? 0 : 4 * qd + t]) * sc[UNIFORM ? 0 : 4 * qd + t]);
-            }
-          }
-        }
-        // columns past the width of a narrow last tile hold zeros so that a GEMM may read whole slabs
-        {
-          float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * SUPER + tile * TILE + c_local);
-#pragma unroll
-          for (int qd = 0; qd < LANE_COLS / 4; ++qd) dst[qd] = make_float4(e[4 * qd], e[4 * qd + 1], e[4 * qd + 2], e[4 * qd + 3]);
-        }
-        if (a.err_planes) {
-          // the tensor-core update reads the errors as bf16 planes: write them in that form directly
-          uint32_t hp[LANE_COLS / 2], mp[LANE_COLS / 2], lp[LANE_COLS / 2];
-#pragma unroll
-          for (int t = 0; t < LANE_COLS; t += 2) {
-            uint16_t h0, m0, l0, h1, m1, l1;
-            split_bf16x3(e[t], h0, m0, l0);
-            split_bf16x3(e[t + 1], h1, m1, l1);
-            hp[t >> 1] = (uint32_t)h0 | ((uint32_t)h1 << 16);
-            mp[t >> 1] = (uint32_t)m0 | ((uint32_t)m1 << 16);
-            lp[t >> 1] = (uint32_t)l0 | ((uint32_t)l1 << 16);
-          }
-          uint16_t* dst = a.err_planes + (int64_t)r * SUPER + tile * TILE + c_local;
-          reinterpret_cast<uint4*>(dst)[0] = make_uint4(hp[0], hp[1], hp[2], hp[3]);
-          reinterpret_cast<uint4*>(dst)[1] = make_uint4(hp[4], hp[5], hp[6], hp[7]);
-          if (a.n_planes > 1) {
-            reinterpret_cast<uint4*>(dst + a.plane_stride)[0] = make_uint4(mp[0], mp[1], mp[2], mp[3]);
-            reinterpret_cast<uint4*>(dst + a.plane_stride)[1] = make_uint4(mp[4], mp[5], mp[6], mp[7]);
-          }
-          if (a.n_planes > 2) {
-            reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[0] = make_uint4(lp[0], lp[1], lp[2], lp[3]);
-            reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[1] = make_uint4(lp[4], lp[5], lp[6], lp[7]);
+          for (int qd = (t + 1) >> 2; qd < LANE_COLS / 4; ++qd) {
+            const float4 u = *reinterpret_cast<const float4*>(&ud[t * U_ROW_LD + 4 * qd]);
+            const float2 p01 = __ffma2_rn(make_float2(u.x, u.y), e2, make_float2(w[4 * qd], w[4 * qd + 1]));
+            const float2 p23 = __ffma2_rn(make_float2(u.z, u.w), e2, make_float2(w[4 * qd + 2], w[4 * qd + 3]));
+            w[4 * qd] = p01.x; w[4 * qd + 1] = p01.y; w[4 * qd + 2] = p23.x; w[4 * qd + 3] = p23.y;
           }
         }
       }
+      __syncwarp();
       // The sixteen errors of lane lo reach the other lanes of the row, which apply them to their
       // own columns in the same order, with the same FMAs, as a one-column-at-a-time recurrence.
       // (For the lanes in front of lo the staged factor holds zeros; lane lo's own values are
@@ -290,20 +196,65 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
         }
       }
     }
-  }
-  }
-}
 
-// Tiles per launch: SUPER_TILES unless MQ_SWEEP_TILES (1..4) says otherwise (a measurement knob:
-// 1 gives one tile per launch with a rank-128 update after each).
-int super_tiles() {
-  static int n = 0;
-  if (n == 0) {
-    const char* e = getenv("MQ_SWEEP_TILES");
-    const int v = e ? atoi(e) : SUPER_TILES;
-    n = (v >= 1 && v <= SUPER_TILES) ? v : SUPER_TILES;
+    // ---- every lane writes what its sixteen columns produced
+    if (valid) {
+#pragma unroll
+      for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
+        if (c_local + 4 * qd >= nb) continue;
+        const uint32_t q4 = (uint32_t)qacc[2 * qd] | ((uint32_t)qacc[2 * qd + 1] << 16);   // four codes, one per byte, first column lowest
+        *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.C + c0 + 4 * qd) = q4;
+        if (a.deq) {
+          T* dq = static_cast<T*>(a.deq) + (int64_t)r * a.C + c0 + 4 * qd;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float qf = (float)((q4 >> (8 * t)) & 0xFFu);
+            dq[t] = from_float<T>((qf - zr[UNIFORM ? 0 : 4 * qd + t]) * sc[UNIFORM ? 0 : 4 * qd + t]);
+          }
+        }
+      }
+      if (a.packed) {
+        // the compressed-tensors word of columns 8k..8k+7 (column 8k+i at bits 4i..4i+3), written
+        // here so that no separate packing pass has to read the codes back
+#pragma unroll
+        for (int h = 0; h < LANE_COLS / 8; ++h) {
+          if (c_local + 8 * h >= nb) continue;
+          const uint32_t lo4 = (uint32_t)qacc[4 * h] | ((uint32_t)qacc[4 * h + 1] << 16);
+          const uint32_t hi4 = (uint32_t)qacc[4 * h + 2] | ((uint32_t)qacc[4 * h + 3] << 16);
+          a.packed[(int64_t)r * (a.C >> 3) + ((c0 + 8 * h) >> 3)] = (int32_t)pack_nibbles(lo4, hi4);
+        }
+      }
+      // columns past nb of a narrow last tile hold zeros so that the GEMM may read all 128
+      if (a.err_planes) {
+        // the tensor-core update reads the errors as bf16 planes: write them in that form directly
+        uint32_t hp[LANE_COLS / 2], mp[LANE_COLS / 2], lp[LANE_COLS / 2];
+#pragma unroll
+        for (int t = 0; t < LANE_COLS; t += 2) {
+          uint16_t h0, m0, l0, h1, m1, l1;
+          split_bf16x3(e[t], h0, m0, l0);
+          split_bf16x3(e[t + 1], h1, m1, l1);
+          hp[t >> 1] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+          mp[t >> 1] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+          lp[t >> 1] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+        }
+        uint16_t* dst = a.err_planes + (int64_t)r * TILE + c_local;
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(hp[0], hp[1], hp[2], hp[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(hp[4], hp[5], hp[6], hp[7]);
+        if (a.n_planes > 1) {
+          reinterpret_cast<uint4*>(dst + a.plane_stride)[0] = make_uint4(mp[0], mp[1], mp[2], mp[3]);
+          reinterpret_cast<uint4*>(dst + a.plane_stride)[1] = make_uint4(mp[4], mp[5], mp[6], mp[7]);
+        }
+        if (a.n_planes > 2) {
+          reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[0] = make_uint4(lp[0], lp[1], lp[2], lp[3]);
+          reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[1] = make_uint4(lp[4], lp[5], lp[6], lp[7]);
+        }
+      } else {
+        float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * TILE + c_local);
+#pragma unroll
+        for (int qd = 0; qd < LANE_COLS / 4; ++qd) dst[qd] = make_float4(e[4 * qd], e[4 * qd + 1], e[4 * qd + 2], e[4 * qd + 3]);
+      }
+    }
   }
-  return n;
 }
 
 template <int DT>
@@ -336,8 +287,8 @@ int configure_once() {
 }  // namespace
 
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
-  size_t bytes = align_up((size_t)R * SUPER * sizeof(float), 256);
-  if (math == MQ_MATH_TENSOR) bytes += plane_set_bytes(R, SUPER, split) + plane_set_bytes(C, C, split);
+  size_t bytes = align_up((size_t)R * TILE * sizeof(float), 256);
+  if (math == MQ_MATH_TENSOR) bytes += plane_set_bytes(R, TILE, split) + plane_set_bytes(C, C, split);
   return bytes;
 }
 
@@ -346,25 +297,25 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
                void* deq, const float* Worig, int64_t ldwo, int math, int split, Workspace& ws, cudaStream_t st,
                const float* col_div, int32_t* packed) {
   // col_div (tensor math only): above its diagonal 128-blocks Uhat holds the factor before its
-  // columns were divided by col_div; whoever reads those blocks divides (the plane split, and the
-  // sweep kernel for the part inside a super-block).  The diagonal blocks are already scaled.
+  // columns were divided by col_div; the plane split divides where it reads it.  The diagonal
+  // blocks, which the tiles read, are already scaled.
   MQ_TRY(configure_once());
-  float* err = ws.take<float>((size_t)R * SUPER);
+  float* err = ws.take<float>((size_t)R * TILE);
   MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
   Engine eng(math, split, ws, st);
-  // Tensor path: the factor is cut into transposed planes once (row n, k -> U[k][n]); the update
-  // behind super-block [s0, s1) reads the window k in [s0, s1), rows n >= s1 of those planes, and
-  // the sweep kernel writes its errors as planes itself.  No per-block conversion passes.
+  // Tensor path: the factor is cut into transposed planes once (row n, k -> U[k][n]); the lazy
+  // update of tile i1 then reads the window k in [i1, i1+128), rows n >= i2 of those planes,
+  // and the sweep kernel writes its errors as planes itself.  No per-tile conversion passes.
   PlaneSet err_set, u_set;
   const bool tensor = math == MQ_MATH_TENSOR;
   if (tensor) {
     MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "mq_gptq_sweep: split must be 1, 2 or 3 (got %d)", split);
-    uint16_t* ep = ws.take<uint16_t>(plane_set_bytes(R, SUPER, split) / 2);
+    uint16_t* ep = ws.take<uint16_t>(plane_set_bytes(R, TILE, split) / 2);
     uint16_t* up = ws.take<uint16_t>(plane_set_bytes(C, C, split) / 2);
     MQ_REQUIRE(ep && up, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small for the operand planes");
     err_set.base = ep; err_set.planes = split; err_set.rows_pad = (int)pad_rows(R); err_set.total_rows = err_set.rows_pad;
-    err_set.K_pad = SUPER;
-    // the updates read Uhat[s0:s1, s1:]: only blocks strictly above the diagonal
+    err_set.K_pad = TILE;
+    // the lazy updates read Uhat[i1:i2, i2:]: only blocks strictly above the diagonal
     MQ_TRY(make_planes_f32(Uhat, 1, ldu, (int)C, (int)C, split, up, &u_set, st, true, col_div));
   }
   SweepArgs sa;
@@ -378,25 +329,23 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   sa.deq = deq; sa.err = err;
   sa.Worig = Worig; sa.ldwo = ldwo;
   sa.err_planes = tensor ? err_set.base : nullptr;
-  sa.plane_stride = tensor ? err_set.total_rows * (int64_t)SUPER : 0;
+  sa.plane_stride = tensor ? err_set.total_rows * (int64_t)TILE : 0;
   sa.n_planes = split;
-  sa.col_div = col_div;
+  sa.bits = bits;
   const bool uniform = group % LANE_COLS == 0;
-  // every CTA stages the tiles of the factor once and then walks row groups: no more CTAs than
+  // every CTA stages the tile of the factor once and then walks row groups: no more CTAs than
   // two per SM, so that a tall layer does not stage the same tile thousands of times
   const int64_t row_groups = ceil_div(R, ROWS_PER_CTA);
   const int grid = (int)(row_groups < 2 * 148 ? row_groups : 2 * 148);
-  const int64_t super_width = (int64_t)super_tiles() * TILE;
-  for (int64_t s0 = 0; s0 < C; s0 += super_width) {
-    const int sbw = (int)((C - s0) < super_width ? (C - s0) : super_width);
+  for (int64_t i1 = 0; i1 < C; i1 += TILE) {
+    const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
     {
-      // The kernel stages its first tile of the factor before it waits for its predecessor: only a
-      // launch that follows this loop's own update (which writes W, never the factor) may be chained.
-      const bool chained = s0 > 0;
-      // bytes the super-block must move: W in, codes out, errors out, the triangles of Uhat once;
-      // flop: the serial in-tile updates plus the cross-tile updates inside the super-block
-      ProfScope prof(PROF_SWEEP_TILE, (double)R * sbw * (4.0 + 1.0 + 4.0) + 2.0 * sbw * TILE, (double)R * sbw * (sbw - 1), st);
-      sa.i1 = (int)s0; sa.nb = sbw;
+      // The kernel stages its tile of the factor before it waits for its predecessor: only a launch
+      // that follows this loop's own update (which writes W, never the factor) may be chained.
+      const bool chained = i1 > 0;
+      // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
+      ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
+      sa.i1 = (int)i1; sa.nb = nb;
       switch (out_dtype) {
         case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
         case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
@@ -404,19 +353,18 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       }
     }
     MQ_LAUNCH_CHECK();
-    const int64_t s1 = s0 + sbw;
-    if (s1 < C) {
-      // W[:, s1:] += E Uhat[s0:s1, s1:]                         src/gptq_loop.py:148, four blocks at a time
+    const int64_t i2 = i1 + nb;
+    if (i2 < C) {
       GemmDesc g;
-      g.A = err; g.a_rs = SUPER; g.a_cs = 1;
-      g.B = Uhat + s0 * ldu + s1; g.b_rs = ldu; g.b_cs = 1;
-      g.C = W + s1; g.ldc = ldw;
-      g.M = (int)R; g.N = (int)(C - s1); g.K = sbw;
+      g.A = err; g.a_rs = TILE; g.a_cs = 1;
+      g.B = Uhat + i1 * ldu + i2; g.b_rs = ldu; g.b_cs = 1;
+      g.C = W + i2; g.ldc = ldw;
+      g.M = (int)R; g.N = (int)(C - i2); g.K = nb;
       g.alpha = 1.0f; g.beta = 1.0f;
       if (tensor) {
         PlaneSet b = u_set;
-        b.row0 = s1;
-        b.k0 = (int)s0;
+        b.row0 = i2;
+        b.k0 = (int)i1;
         MQ_TRY(gemm_tensor_planes(g, err_set, b, st));
       } else {
         MQ_TRY(eng.gemm(g));

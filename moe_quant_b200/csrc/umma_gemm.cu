@@ -24,7 +24,6 @@
 // the kernel still frees its TMEM and returns.
 #include <cuda.h>
 #include <cstring>
-#include <mutex>
 
 #include "engine.cuh"
 #include "profile.cuh"
@@ -1112,30 +1111,6 @@ int configure_once() {
   return MQ_OK;
 }
 
-// How many different streams issued rank-128 updates among the last few hundred of them (a layer
-// issues 110 on its stream before the next layer's stream takes over).
-int concurrent_streams(cudaStream_t st) {
-  static std::mutex mu;
-  static cudaStream_t seen[16];
-  static unsigned long long stamp[16];
-  static unsigned long long tick = 0;
-  constexpr unsigned long long WINDOW = 1024;
-  std::lock_guard<std::mutex> lock(mu);
-  ++tick;
-  int slot = -1, oldest = 0;
-  for (int i = 0; i < 16; ++i) {
-    if (stamp[i] != 0 && seen[i] == st) slot = i;
-    if (stamp[i] < stamp[oldest]) oldest = i;
-  }
-  if (slot < 0) slot = oldest;
-  seen[slot] = st;
-  stamp[slot] = tick;
-  int n = 0;
-  for (int i = 0; i < 16; ++i)
-    if (stamp[i] != 0 && tick - stamp[i] < WINDOW) ++n;
-  return n;
-}
-
 int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStream_t st) {
   MQ_TRY(configure_once());
   CUtensorMap map_a, map_b;
@@ -1184,21 +1159,6 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
         const double waves = (double)((ctas + 147) / 148);
         const double cost = waves * (4.0 + cand);
         if (cost < best) { best = cost; run = cand; }
-      }
-      // Several independent callers at once (layers on different streams): their kernels share the
-      // GPU anyway, and the same update as fewer, longer CTAs loads its stationary A planes less
-      // often and leaves SMs to the other streams (measured with 8 streams: +5 % layers/s at a cap
-      // of 74 CTAs; alone the same cap costs 17 %, hence only then).
-      if (concurrent_streams(st) >= 4) {
-        const int cap = 74;
-        for (int cand = 1; cand <= 64; ++cand) {
-          long long ctas = 0;
-          for (int m = 0; m < m_tiles; ++m) {
-            const int cnt = d.upper_tiles_only ? n_tiles - m : n_tiles;
-            if (cnt > 0) ctas += (cnt + cand - 1) / cand;
-          }
-          if (ctas <= cap) { run = cand; break; }
-        }
       }
     }
     dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);

@@ -31,21 +31,27 @@ constexpr int NB = 128;  // panel width
 
 // ------------------------------------------------------------------ diagonal block
 // D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
-// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers, and the 16 threads
-// of one tile column are the 16 lanes of a half-warp.  The 128 pivots are taken 8 at a time.
-// For leaf kt the half-warp of tile column kt works alone: the owner of the diagonal tile
-// publishes it, every lane factors its own copy in registers (the same arithmetic 16 times,
-// no communication inside the chain of 8 pivots) and applies each pivot to its 8 rows of the
-// panel above the leaf as soon as it exists, so the panel solve fills the latency gaps of the
-// pivot chain.  One block-wide barrier per leaf; then every remaining upper tile takes one
-// rank-8 update from the panel, which is double buffered so that the next leaf's half-warp
-// may write its panel while slower warps still read this one.
+// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers, and the 16 tiles of a
+// tile column are the lanes of one half-warp.  The 128 pivots are taken 8 at a time (a "leaf",
+// tile column 15 first).  One warp's instruction stream runs at a fraction of an instruction
+// per cycle here (every step depends on the one before), so a leaf is arranged to put as few
+// instructions as possible in any one stream:
+//   1. the half-warp that holds tile column kt writes its tiles to shared memory, one row of
+//      the block per shared-memory column;
+//   2. thread r of the first four warps takes ROW r of that column strip: it factors its own copy
+//      of the 8x8 leaf in registers (the same arithmetic in every thread, no communication
+//      inside the chain of 8 pivots) and solves its own row against it, 36 operations, instead
+//      of one half-warp solving eight rows per lane; the rows of the leaf itself write the
+//      factored leaf back;
+//   3. the strip, now the panel of T above the leaf plus the leaf's factor, is read back by
+//      the half-warp that owns it, and every remaining upper tile takes one rank-8 update from it.
+// The strip is double buffered so that the next leaf's half-warp may write while slower warps
+// still read this one.
 constexpr int PAN_LD = NB + 4;
 
 __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                             int k_global, mq_layer_flags* flags) {
-  __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of T, rows above the leaf
-  __shared__ __align__(16) float leaf_pub[8][8];     // the diagonal tile before its factorisation
+  __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of the strip
   chain_wait();
   chain_release();
   const int t = threadIdx.x;
@@ -76,72 +82,83 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
   }
   for (int kt = 15; kt >= 0; --kt) {
     const int buf = kt & 1;
-    if (warp == (kt >> 1)) {
-      if (tc == kt && tr == kt) {
+    // ---- 1. the strip of tile column kt goes to shared memory, transposed
+    if (tc == kt && tr <= kt) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          *reinterpret_cast<float4*>(&leaf_pub[i][0]) = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
-          *reinterpret_cast<float4*>(&leaf_pub[i][4]) = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
-        }
-      }
-      __syncwarp();
-      if (tc == kt && tr <= kt) {
-        float L[8][8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 lo = *reinterpret_cast<const float4*>(&leaf_pub[i][0]);
-          const float4 hi = *reinterpret_cast<const float4*>(&leaf_pub[i][4]);
-          L[i][0] = lo.x; L[i][1] = lo.y; L[i][2] = lo.z; L[i][3] = lo.w;
-          L[i][4] = hi.x; L[i][5] = hi.y; L[i][6] = hi.z; L[i][7] = hi.w;
-        }
-        // The 8 pivots are one straight line of code (no branch), so that the scheduler can
-        // put the panel arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.
-        // The owner of the diagonal tile runs the panel arithmetic on its own tile too; that
-        // copy is discarded below.
-        int fail = 0;
-#pragma unroll
-        for (int kk = 7; kk >= 0; --kk) {
-          float d = L[kk][kk];
-          const bool bad = !(d > 0.0f);  // also catches NaN
-          fail = (bad && fail == 0) ? kk + 1 : fail;
-          d = bad ? 1.0f : d;
-          float r = rsqrtf(d);
-          r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
-          L[kk][kk] = d * r;
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (i < kk) L[i][kk] *= r;
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (i <= j && j < kk) L[i][j] = fmaf(-L[i][kk], L[j][kk], L[i][j]);
-          // rows above the leaf: p_kk = a_kk / T[kk][kk]; a_j -= p_kk T[j][kk]  (j < kk)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float pv = a[i][kk] * r;
-            a[i][kk] = pv;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j < kk) a[i][j] = fmaf(-pv, L[j][kk], a[i][j]);
-          }
-        }
-        if (tr < kt) {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-            *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
-          }
-        } else {
-          if (fail != 0 && kt * 8 + fail - 1 < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + fail);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) a[i][j] = (i <= j) ? L[i][j] : 0.0f;
-        }
+      for (int kk = 0; kk < 8; ++kk) {
+        *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
+        *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
       }
     }
     __syncthreads();
+    // ---- 2. one row of the strip per thread
+    const int row = t;
+    if (row < kt * 8 + 8) {
+      float L[8][8];   // L[i][j] = leaf element (row 8kt+i, column 8kt+j), upper triangle
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 lo = *reinterpret_cast<const float4*>(&pan[buf][j][kt * 8]);
+        const float4 hi = *reinterpret_cast<const float4*>(&pan[buf][j][kt * 8 + 4]);
+        L[0][j] = lo.x; L[1][j] = lo.y; L[2][j] = lo.z; L[3][j] = lo.w;
+        L[4][j] = hi.x; L[5][j] = hi.y; L[6][j] = hi.z; L[7][j] = hi.w;
+      }
+      float x[8];
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) x[kk] = pan[buf][kk][row];
+      // The 8 pivots are one straight line of code (no branch), so that the scheduler can put
+      // the row arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.  The rows
+      // of the leaf itself run the row arithmetic too; that copy is discarded below.
+      int fail = 0;
+#pragma unroll
+      for (int kk = 7; kk >= 0; --kk) {
+        float d = L[kk][kk];
+        const bool bad = !(d > 0.0f);  // also catches NaN
+        fail = (bad && fail == 0) ? kk + 1 : fail;
+        d = bad ? 1.0f : d;
+        float r = rsqrtf(d);
+        r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
+        L[kk][kk] = d * r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < kk) L[i][kk] *= r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (i <= j && j < kk) L[i][j] = fmaf(-L[i][kk], L[j][kk], L[i][j]);
+        // this row above the leaf: p_kk = x_kk / T[kk][kk]; x_j -= p_kk T[j][kk]  (j < kk)
+        const float pv = x[kk] * r;
+        x[kk] = pv;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < kk) x[j] = fmaf(-pv, L[j][kk], x[j]);
+      }
+      const int li = row - kt * 8;   // >= 0: a row of the leaf, which gets the factor instead
+      if (li >= 0) {
+        if (li == 0 && fail != 0 && kt * 8 + fail - 1 < nb) atomicCAS(&flags->not_positive, 0, k_global + kt * 8 + fail);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          float v = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i == li && i <= kk) v = L[i][kk];
+          x[kk] = v;
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) pan[buf][kk][row] = x[kk];
+    }
+    __syncthreads();
+    // ---- 3. the owners take the strip back; everything in front of it takes its rank-8 update
+    if (tc == kt && tr <= kt) {
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const float4 lo = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8]);
+        const float4 hi = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8 + 4]);
+        a[0][kk] = lo.x; a[1][kk] = lo.y; a[2][kk] = lo.z; a[3][kk] = lo.w;
+        a[4][kk] = hi.x; a[5][kk] = hi.y; a[6][kk] = hi.z; a[7][kk] = hi.w;
+      }
+    }
     if (tr <= tc && tc < kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
@@ -169,7 +186,7 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
-      if (tr <= tc) {  // the diagonal tiles were zeroed below their diagonal when they were factored
+      if (tr <= tc) {  // the diagonal tiles came back from the strip with zeros below their diagonal
         lo = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
         hi = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
       }

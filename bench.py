@@ -592,8 +592,9 @@ def cx_no_cpu(cx):
 def parity_sample(cx):
     """Untimed: one of the benchmark's own experts (its ragged token count) quantized once, the
     first 128 rows compared with the CPU oracle fed with the same Hessian.  Beside the engine's
-    figure stands the oracle's own noise floor on this Hessian: its fp32 route against the same
-    route with the factor computed in fp64.  (With far fewer tokens than input channels the
+    figure stand the oracle's own distance from exact arithmetic on this Hessian (its fp32 route
+    against the same route with the factor computed in fp64) and the engine's agreement with that
+    exact-factor route.  (With far fewer tokens than input channels the
     damped Hessian is so ill conditioned that a code on a rounding boundary flips with the last
     bits of the factor, and one flip changes a third of the codes behind it in that row.)"""
     from oracle import gptq_oracle as O
@@ -620,7 +621,9 @@ def parity_sample(cx):
         sc, zr, maxq = O.symmetric_grid(Wf, GROUP, BITS, Wc.dtype)
         Q = O.gptq_sweep(Wf.t().contiguous(), U, sc.repeat_interleave(GROUP, -1).t().contiguous(),
                          zr.repeat_interleave(GROUP, -1).t().contiguous(), maxq, Wc.dtype, 128)
-        out["oracle_fp32_vs_fp64_factor"] = O.code_agreement(Q.t().contiguous().to(torch.uint8), want["qweight"])
+        exact = Q.t().contiguous().to(torch.uint8)
+        out["oracle_fp32_vs_exact_factor"] = O.code_agreement(exact, want["qweight"])
+        out["code_agreement_with_exact_factor"] = O.code_agreement(q[:rows].cpu(), exact)
     return out
 
 

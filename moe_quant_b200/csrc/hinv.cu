@@ -45,13 +45,17 @@ constexpr int NB = 128;  // panel width
 //      factored leaf back;
 //   3. the strip, now the panel of T above the leaf plus the leaf's factor, is read back by
 //      the half-warp that owns it, and every remaining upper tile takes one rank-8 update from it.
-// The strip is double buffered so that the next leaf's half-warp may write while slower warps
+// The solved strip is double buffered so that the next leaf may be written while slower warps
 // still read this one.
 constexpr int PAN_LD = NB + 4;
 
 __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                             int k_global, mq_layer_flags* flags) {
-  __shared__ __align__(16) float pan[2][8][PAN_LD];  // pan[buf][kk][row]: column 8kt+kk of the strip
+  // raw[kk][row]: column 8kt+kk of the strip as its owners hold it; pan[buf][kk][row]: the same
+  // strip solved (the panel of T above the leaf, and the leaf's factor).  Two arrays, because a
+  // thread may still be reading the raw leaf when another has its row ready.
+  __shared__ __align__(16) float raw[8][PAN_LD];
+  __shared__ __align__(16) float pan[2][8][PAN_LD];
   chain_wait();
   chain_release();
   const int t = threadIdx.x;
@@ -86,8 +90,8 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
     if (tc == kt && tr <= kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-        *reinterpret_cast<float4*>(&pan[buf][kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
+        *reinterpret_cast<float4*>(&raw[kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
+        *reinterpret_cast<float4*>(&raw[kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
       }
     }
     __syncthreads();
@@ -97,14 +101,14 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
       float L[8][8];   // L[i][j] = leaf element (row 8kt+i, column 8kt+j), upper triangle
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float4 lo = *reinterpret_cast<const float4*>(&pan[buf][j][kt * 8]);
-        const float4 hi = *reinterpret_cast<const float4*>(&pan[buf][j][kt * 8 + 4]);
+        const float4 lo = *reinterpret_cast<const float4*>(&raw[j][kt * 8]);
+        const float4 hi = *reinterpret_cast<const float4*>(&raw[j][kt * 8 + 4]);
         L[0][j] = lo.x; L[1][j] = lo.y; L[2][j] = lo.z; L[3][j] = lo.w;
         L[4][j] = hi.x; L[5][j] = hi.y; L[6][j] = hi.z; L[7][j] = hi.w;
       }
       float x[8];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) x[kk] = pan[buf][kk][row];
+      for (int kk = 0; kk < 8; ++kk) x[kk] = raw[kk][row];
       // The 8 pivots are one straight line of code (no branch), so that the scheduler can put
       // the row arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.  The rows
       // of the leaf itself run the row arithmetic too; that copy is discarded below.

@@ -197,9 +197,14 @@ __device__ __forceinline__ void issue_slab_mn(uint32_t tmem_d, uint32_t a_tile, 
 // i + j < PLANES.  The issuing thread must feed the tensor pipe one MMA every ~64 cycles, so
 // the loops are unrolled at compile time and a descriptor costs one 32-bit add: only the
 // address field (low word) changes between tiles, planes and K steps.
+// The leading product (hi x hi) and the correction products go to two different accumulators,
+// `tmem_d` and `tmem_d + small_off`, which the epilogue adds in fp32.  The corrections are 2^-8 and
+// 2^-16 of the leading term: summed into one accumulator they would each cost it a rounding at
+// full magnitude (48 roundings per 128 of k instead of 8), and the tensor core's accumulation
+// does not round to nearest; kept apart, the small sums keep their own low bits.
 template <int PLANES>
-__device__ __forceinline__ void issue_slab(uint32_t tmem_d, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
-                                           uint32_t& accumulate) {
+__device__ __forceinline__ void issue_slab(uint32_t tmem_d, uint32_t small_off, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+                                           uint32_t& accumulate, uint32_t& accumulate_small) {
   const uint64_t a0 = kmajor_sw128_desc(a_tile), b0 = kmajor_sw128_desc(b_tile);
   const uint32_t hi = (uint32_t)(a0 >> 32);
   const uint32_t a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;
@@ -212,19 +217,36 @@ __device__ __forceinline__ void issue_slab(uint32_t tmem_d, uint32_t a_tile, uin
         if (ti + tj < PLANES) {
           const uint64_t ad = ((uint64_t)hi << 32) | (uint64_t)(a_lo + (uint32_t)((ti * PLANE_TILE_BYTES + kk * 32) >> 4));
           const uint64_t bd = ((uint64_t)hi << 32) | (uint64_t)(b_lo + (uint32_t)((tj * PLANE_TILE_BYTES + kk * 32) >> 4));
-          umma_bf16(tmem_d, ad, bd, idesc, accumulate);
-          accumulate = 1;
+          if (ti + tj == 0) {
+            umma_bf16(tmem_d, ad, bd, idesc, accumulate);
+            accumulate = 1;
+          } else {
+            umma_bf16(tmem_d + small_off, ad, bd, idesc, accumulate_small);
+            accumulate_small = 1;
+          }
         }
       }
     }
   }
 }
 
-__device__ __forceinline__ void issue_slab_any(int planes, uint32_t tmem_d, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
-                                               uint32_t& accumulate) {
-  if (planes == 3) issue_slab<3>(tmem_d, a_tile, b_tile, idesc, accumulate);
-  else if (planes == 2) issue_slab<2>(tmem_d, a_tile, b_tile, idesc, accumulate);
-  else issue_slab<1>(tmem_d, a_tile, b_tile, idesc, accumulate);
+__device__ __forceinline__ void issue_slab_any(int planes, uint32_t tmem_d, uint32_t small_off, uint32_t a_tile, uint32_t b_tile,
+                                               uint32_t idesc, uint32_t& accumulate, uint32_t& accumulate_small) {
+  if (planes == 3) issue_slab<3>(tmem_d, small_off, a_tile, b_tile, idesc, accumulate, accumulate_small);
+  else if (planes == 2) issue_slab<2>(tmem_d, small_off, a_tile, b_tile, idesc, accumulate, accumulate_small);
+  else issue_slab<1>(tmem_d, small_off, a_tile, b_tile, idesc, accumulate, accumulate_small);
+}
+
+// 32 accumulator columns of this warp's TMEM lanes; with small_off != 0 the sum of the leading
+// and the correction accumulator.
+__device__ __forceinline__ void tmem_ld32_sum(uint32_t taddr, uint32_t small_off, float (&v)[32]) {
+  tmem_ld32(taddr, v);
+  if (small_off) {
+    float c[32];
+    tmem_ld32(taddr + small_off, c);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += c[i];
+  }
 }
 
 // Epilogue of one 128 x TN tile by the four epilogue warps: C <- alpha * acc + beta * C with the
@@ -236,7 +258,7 @@ __device__ __forceinline__ bool epilogue_tile(const float alpha, const float bet
                                               float* __restrict__ C, const int m0, const int n0,
                                               const int N, const uint32_t tmem_acc, float* stage_base, const int warp,
                                               const int lane, const bool have_acc, const uint32_t acc_bar,
-                                              const uint32_t acc_parity) {
+                                              const uint32_t acc_parity, const uint32_t small_off = 0) {
   const int q = warp & 3;  // TMEM lane quadrant this warp may read
   const int row = m0 + q * 32 + lane;
   const bool vec_ok = (ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
@@ -275,7 +297,7 @@ __device__ __forceinline__ bool epilogue_tile(const float alpha, const float bet
       for (int c = 0; c < 4; ++c) {
         float v[32];
         if (have_acc) {
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128 + c * 32), v);
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128 + c * 32), small_off, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.0f;
@@ -330,7 +352,7 @@ __device__ __forceinline__ bool epilogue_tile(const float alpha, const float bet
       for (int c = 0; c < TN / 32; ++c) {
         float v[32];
         if (have_acc) {
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), small_off, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.0f;
@@ -398,7 +420,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     mbar_init(acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TN);
+  // with more than one plane the correction products get an accumulator of their own
+  const uint32_t small_off = planes > 1 ? (uint32_t)TN : 0u;
+  const uint32_t tmem_cols = planes > 1 ? 2 * TN : TN;
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -424,7 +449,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      uint32_t accumulate = 0;
+      uint32_t accumulate = 0, accumulate_small = 0;
       bool ok = true;
       for (int s = 0; s < n_slabs && ok; ++s) {
         const int st = s % p.stages;
@@ -433,8 +458,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
         tc_fence_after();
         const uint32_t a_base = smem_base + st * stage_bytes;
         const uint32_t b_base = a_base + planes * PLANE_TILE_BYTES;
-        if (TN == 128) issue_slab_any(planes, tmem_acc, a_base, b_base, idesc, accumulate);
-        else issue_slab<1>(tmem_acc, a_base, b_base, idesc, accumulate);
+        if (TN == 128) issue_slab_any(planes, tmem_acc, small_off, a_base, b_base, idesc, accumulate, accumulate_small);
+        else issue_slab<1>(tmem_acc, 0u, a_base, b_base, idesc, accumulate, accumulate_small);
         umma_commit(empty0 + 8 * st);  // the stage is free once these MMAs have read it
       }
       umma_commit(acc_bar);  // arrives when every MMA issued above has completed
@@ -443,13 +468,14 @@ __global__ void __launch_bounds__(GEMM_THREADS) umma_gemm_kernel(const __grid_co
     // every MMA has completed when the accumulator barrier fires, so the operand stages are
     // free: stage 0 becomes the staging tiles
     epilogue_tile<TN>(p.alpha, p.beta, p.ldc, p.M, p.mirror, p.C + (int64_t)b * p.c_bs, m0, n0, N, tmem_acc,
-                      reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))), warp, lane, n_slabs > 0, acc_bar, 0);
+                      reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))), warp, lane, n_slabs > 0, acc_bar, 0,
+                      small_off);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, TN);
+    tmem_dealloc(tmem_acc, tmem_cols);
   }
 }
 
@@ -556,7 +582,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_gemm_persistent_kernel(c
       if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 32);
       if (!ok) break;
       tc_fence_after();
-      uint32_t accumulate = 0;
+      uint32_t accumulate = 0, unused_small = 0;
       for (int s = 0; s < n_slabs && ok; ++s, ++it) {
         const int st = it % NST;
         ok = mbar_wait(full0 + 8 * st, (it / NST) & 1, 33);
@@ -565,7 +591,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_gemm_persistent_kernel(c
         if (lane == 0) {
           const uint32_t a_base = smem_base + (uint32_t)st * STAGE;
           if (DIRECT) issue_slab_mn(tmem_acc + (uint32_t)(acc * TN), a_base, a_base + PLANE_TILE_BYTES, p.idesc, accumulate);
-          else issue_slab<1>(tmem_acc + (uint32_t)(acc * TN), a_base, a_base + PLANE_TILE_BYTES, p.idesc, accumulate);
+          else issue_slab<1>(tmem_acc + (uint32_t)(acc * TN), 0u, a_base, a_base + PLANE_TILE_BYTES, p.idesc, accumulate, unused_small);
           umma_commit(empty0 + 8 * st);
         }
         __syncwarp();
@@ -644,7 +670,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 2 * TILE_N);
+  // two alternating tiles, each with a leading and (more than one plane) a correction accumulator
+  const uint32_t small_off = p.planes > 1 ? (uint32_t)TILE_N : 0u;
+  const uint32_t acc_stride = p.planes > 1 ? 2u * TILE_N : (uint32_t)TILE_N;
+  const uint32_t tmem_cols = 2u * acc_stride;
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -687,7 +717,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
       if (i >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((i >> 1) - 1) & 1, 13);
       if (!ok) break;
       tc_fence_after();
-      uint32_t accumulate = 0;
+      uint32_t accumulate = 0, accumulate_small = 0;
       for (int s = 0; s < n_slabs && ok; ++s, ++it) {
         const int st = it & 1;
         ok = mbar_wait(b_full + 8 * st, (it >> 1) & 1, 14);
@@ -696,7 +726,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         if (lane == 0) {
           const uint32_t a_tile = smem_base + (uint32_t)(s * planes) * PLANE_TILE_BYTES;
           const uint32_t b_tile = b_base + (uint32_t)st * b_stage_bytes;
-          issue_slab_any(planes, tmem_acc + (uint32_t)(acc * TILE_N), a_tile, b_tile, idesc, accumulate);
+          issue_slab_any(planes, tmem_acc + (uint32_t)acc * acc_stride, small_off, a_tile, b_tile, idesc, accumulate, accumulate_small);
           umma_commit(b_empty + 8 * st);  // the stage is free once these MMAs have read it
         }
         __syncwarp();
@@ -732,7 +762,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
 #pragma unroll 1
         for (int c = 0; c < TILE_N / 32; ++c, ++chunk) {
           float v[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_stride + (uint32_t)(c * 32), small_off, v);
           if (c == TILE_N / 32 - 1) {
             // the accumulator is in registers: hand its TMEM columns back to the MMA warp
             tc_fence_before();
@@ -787,7 +817,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
 #pragma unroll
         for (int c = 0; c < TILE_N / 32; ++c) {
           float v[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_stride + (uint32_t)(c * 32), small_off, v);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<float4*>(&stage[lane * STAGE_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -813,7 +843,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
         for (int c = 0; c < TILE_N / 32; ++c) {
           const int col0 = n0 + c * 32;
           float v[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * TILE_N + c * 32), v);
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_stride + (uint32_t)(c * 32), small_off, v);
           if (row < p.M && col0 < p.N) {
             float* dst = dst_row + c * 32;
 #pragma unroll
@@ -836,7 +866,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, 2 * TILE_N);
+    tmem_dealloc(tmem_acc, tmem_cols);
   }
 }
 

@@ -303,3 +303,34 @@ def test_quantize_packed_writes_the_words_in_the_sweep(cuda, R, C, g, dtype):
     out2 = h.quantize_packed(4)
     want2 = O.pack_weight({"qweight": out2["qweight"].cpu(), "scale": out2["scale"].cpu(), "zero": out2["zero"].cpu()}, 4, True, g)
     assert torch.equal(out2["weight_packed"].cpu(), want2["weight_packed"])
+
+
+def test_repeated_quantization_is_bit_identical_and_clean(cuda):
+    """The same layer many times over, alone and on several streams at once: every run must give the
+    same codes bit for bit and raise no Hessian flag (a race inside a kernel shows up as a rare
+    non-positive pivot or a handful of different codes)."""
+    from moe_quant_b200 import quantize_many
+    R, C, N = 512, 2048, 1000
+    g = torch.Generator(device="cuda").manual_seed(3)
+    W = (0.02 * torch.randn(R, C, generator=g, device=cuda)).to(torch.bfloat16)
+    X = (torch.randn(N, C, generator=g, device=cuda) * torch.exp(torch.randn(C, generator=g, device=cuda))).to(torch.bfloat16)
+    H = torch.zeros(C, C, device=cuda)
+    ops.hessian_accum(H, X, 0.0, 2.0 / N)
+
+    def handles(n):
+        out = []
+        for _ in range(n):
+            h = GPTQ(_layer(W, cuda), 128, True, 1e-2, 128)
+            h.H, h.num_samples = H.clone(), N
+            out.append(h)
+        return out
+
+    first = handles(1)[0].quantize(4)
+    seq = handles(40)
+    for h in seq:
+        q, s, _ = h.quantize(4)
+        assert torch.equal(q, first[0]) and torch.equal(s, first[1])
+    par = handles(48)
+    for q, s, _ in quantize_many(par, 4, streams=8):
+        assert torch.equal(q, first[0]) and torch.equal(s, first[1])
+    assert not any(h.has_hessian_issues() for h in seq + par)

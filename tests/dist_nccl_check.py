@@ -4,10 +4,13 @@
         --master-port 29511 tests/dist_nccl_check.py
 
 Every rank accumulates the Hessian of its own slice of the calibration tokens (slices of
-different length), `quantize` all-reduces it, rank 0 quantizes, results are broadcast.  Checks:
-the reduced Hessian equals the Hessian of all tokens, every rank ends with identical tensors,
-and the codes agree with a single-GPU run on all tokens.  Not collected by pytest (it needs
-more than one device); the CPU twin of this protocol test is tests/test_dist_gloo.py.
+different length).  Part 1, the reference's scheme: `quantize` all-reduces it, rank 0 quantizes,
+results are broadcast.  Part 2, the owner-rank scheme (`gptq.quantize_shared`): five layers of
+different shapes, each Hessian reduced to its owner, owners quantize side by side, results
+broadcast from their owners.  Checks: the reduced Hessian equals the Hessian of all tokens,
+every rank ends with identical tensors, and the codes agree with a single-GPU run on all
+tokens.  Not collected by pytest (it needs more than one device); the CPU twin of this protocol
+test is tests/test_dist_gloo.py.
 """
 import os
 import sys
@@ -57,8 +60,43 @@ def main():
     if rank == 0:
         print(f"world {world}: reduced-H rel err {rel:.2e}, identical on all ranks {same}, "
               f"agreement with single-GPU run {agree:.5f} -> {'OK' if flag.item() else 'FAIL'}")
+
+    # ---- part 2: owner-rank scheme on five layers
+    from moe_quant_b200.gptq import quantize_shared, shared_layer_owners
+    shapes = [(384, 1024), (1024, 512), (192, 1024), (2048, 256), (512, 2048)]
+    Ws = [synthetic.layer_weight(r, c, 30 + i, torch.bfloat16).to(dev) for i, (r, c) in enumerate(shapes)]
+    Xs = [synthetic.activations(N, c, 40 + i, torch.bfloat16).to(dev) for i, (_, c) in enumerate(shapes)]
+
+    def handles(distributed):
+        out = []
+        for w in Ws:
+            layer = nn.Linear(w.shape[1], w.shape[0], bias=False, dtype=torch.bfloat16, device=dev)
+            layer.weight.data = w.clone()
+            out.append(GPTQ(layer, 128, True, 1e-2, 128, is_distributed=distributed))
+        return out
+
+    hs, ref = handles(True), handles(False)
+    for h, r, x in zip(hs, ref, Xs):
+        h.update(x[cuts[rank]: cuts[rank + 1]])
+        r.update(x)
+    owners = shared_layer_owners(hs, world)
+    results = quantize_shared(hs, 4)
+    ok2 = len(set(owners)) == min(world, len(shapes))
+    worst = 1.0
+    for (q, s, z), r in zip(results, ref):
+        q1, s1, _ = r.quantize(4)
+        gathered = [torch.empty_like(q) for _ in range(world)]
+        dist.all_gather(gathered, q)
+        ok2 &= all(torch.equal(gathered[0], t) for t in gathered) and torch.equal(s, s1)
+        worst = min(worst, float((q == q1).double().mean()))
+    ok2 &= worst >= 0.995 and not any(h.has_hessian_issues() for h in hs)
+    flag2 = torch.tensor([float(ok2)], device=dev)
+    dist.all_reduce(flag2, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"world {world}: owner-rank scheme, owners {owners}, worst agreement with single-GPU runs {worst:.5f} "
+              f"-> {'OK' if flag2.item() else 'FAIL'}")
     dist.destroy_process_group()
-    sys.exit(0 if flag.item() else 1)
+    sys.exit(0 if flag.item() and flag2.item() else 1)
 
 
 if __name__ == "__main__":

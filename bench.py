@@ -669,20 +669,59 @@ def wl_down_proj(cx):
         one, ms1 = _time_layers(cx, build, 4, 1)
         out["groups"][str(g)] = {"layers_per_s": many, "layers_per_s_one_stream": one,
                                  "fp32_equiv_tflops_one_stream": layer_flop(rows, cols) / (ms1 / 4 / 1e3) / 1e12}
-    # packing alone: 16 different code matrices (235 MB, larger than L2), one launch each
+    # quantize + separate packing pass against the sweep that writes the packed words itself (g = 128, one stream)
+    def build128():
+        h = GPTQ(_linear(W), 128, True, 1e-2, 128)
+        h.H = H.clone()
+        h.num_samples = toks
+        return h
+
+    def timed_layers(fn, n=6):
+        fn(build128())
+        torch.cuda.synchronize()
+        hs = [build128() for _ in range(n)]
+        torch.cuda.synchronize()
+        e0, e1 = _event_pair()
+        e0.record()
+        keep = [fn(h) for h in hs]
+        e1.record()
+        torch.cuda.synchronize()
+        del keep
+        return e0.elapsed_time(e1) / n
+
+    ms_two = timed_layers(lambda h: ops.pack_int4(h.quantize(BITS)[0]))
+    ms_fused = timed_layers(lambda h: h.quantize_packed(BITS))
+    out["quantize_then_pack_ms"] = ms_two
+    out["quantize_packed_fused_ms"] = ms_fused
+
+    # packing alone: 16 different code matrices (235 MB, larger than L2), one launch each, replayed
+    # from a CUDA graph so that the device time is not the time Python needs to issue a launch
+    from moe_quant_b200 import _lib
     codes = [torch.randint(0, 16, (rows, cols), dtype=torch.uint8, device=dev) for _ in range(16)]
-    for c in codes:
-        ops.pack_int4(c)
+    words = [torch.empty(rows, cols // 8, dtype=torch.int32, device=dev) for _ in range(16)]
+    L = _lib.lib()
+
+    def pack_all():
+        st = _lib.stream_ptr(dev)
+        for c, w in zip(codes, words):
+            _lib.check(L.mq_pack_int4(c.data_ptr(), rows, cols, None, 0, w.data_ptr(), st))
+
+    pack_all()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pack_all()
+    graph.replay()
     torch.cuda.synchronize()
     e0, e1 = _event_pair()
     e0.record()
-    for _ in range(4):
-        for c in codes:
-            ops.pack_int4(c)
+    for _ in range(8):
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / 64
+    us = e0.elapsed_time(e1) * 1e3 / (8 * 16)
     gbs = 1.5 * rows * cols / (us * 1e-6) / 1e9
+    assert torch.equal(words[3], ops.pack_int4(codes[3]))
     out["pack"] = {"us_per_launch": us, "gbs": gbs, "bytes_per_launch": 1.5 * rows * cols,
                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": cx.peaks["hbm"], "unit": "GB/s",
                                 "frac": gbs / cx.peaks["hbm"], "peak_source": cx.peaks["source"]}}

@@ -150,13 +150,17 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A scratch buffer per (device, current stream) that only ever grows.  Work is
-    stream-ordered, so consecutive calls on one stream may share it; calls on different
-    streams may overlap on the GPU and therefore get different buffers."""
+    """A scratch buffer per (device, current stream).  Work is stream-ordered, so consecutive
+    calls on one stream may share it; calls on different streams may overlap on the GPU and
+    therefore get different buffers.  The buffer grows on demand; one of more than 1 GB is
+    replaced by a smaller one when a call needs less than a quarter of it (a single very wide
+    layer would otherwise pin gigabytes on every stream it ever ran on).  The caching allocator
+    keeps the old block alive until the stream's queued work has used it."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     key = (index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
+    oversized = buf is not None and buf.numel() > (1 << 30) and 4 * max(int(nbytes), 1) < buf.numel()
+    if buf is None or buf.numel() < nbytes or oversized:
         _workspaces[key] = None
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         _workspaces[key] = buf

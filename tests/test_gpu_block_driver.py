@@ -3,6 +3,7 @@ refresh activations) on a small DeepSeek-shaped MoE block, each layer checked ag
 fed with the very activations the hooks saw, then the compressed-tensors shard written from
 the saved results."""
 import copy
+import re
 import os
 
 import pytest
@@ -137,3 +138,16 @@ def test_routed_expert_regex_matches_reference_names():
     assert re.search(ROUTED_EXPERTS_REGEX, "model.layers.3.mlp.experts.17.up_proj")
     assert not re.search(ROUTED_EXPERTS_REGEX, "model.layers.3.mlp.shared_experts.up_proj")
     assert not re.search(ROUTED_EXPERTS_REGEX, "model.layers.3.self_attn.o_proj")
+
+
+def test_non_main_rank_writes_its_experts_but_not_the_shared_layers(cuda, tmp_path, monkeypatch):
+    """Shared layers hold the same result on every rank and are written by rank 0 only
+    (quant.py:321); a routed expert is written by the rank that quantized it (quant.py:375-380)."""
+    from moe_quant_b200 import dist_utils
+    block = SyntheticMoEBlock(hidden=256, inter=128, n_experts=4, top_k=2, seed=9).to(torch.bfloat16).to(cuda)
+    monkeypatch.setattr(dist_utils, "is_main", lambda: False)
+    save_dir = str(tmp_path / "rank1")
+    res = quantize_block(block, _inputs(cuda, n_seq=2), prefix="model.layers.0.", save_dir=save_dir, streams=2)
+    written = set(os.listdir(save_dir))
+    experts = {"model.layers.0." + n for n in res["layers"] if re.search(ROUTED_EXPERTS_REGEX, "model.layers.0." + n)}
+    assert experts and written == experts

@@ -144,9 +144,10 @@ size_t mq_hinv_upper_workspace_bytes(int64_t C, int math, int split);
  * Utilde is the inverse of Uhat.  mq_gptq_sweep accepts it directly (W_original != NULL), which
  * saves the triangular inverse: that is what mq_quantize_layer does.  Non-positive pivot:
  * flags->not_positive is set and the result is I.
- * workspace: mq_gemm_workspace_bytes(C, C, 128, math, split) + 256 + 4*C bytes.  */
+ * workspace: mq_chol_unit_factor_workspace_bytes(C, math, split).  */
 int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag_out, int math, int split,
                         mq_layer_flags* flags, void* workspace, size_t workspace_bytes, void* stream);
+size_t mq_chol_unit_factor_workspace_bytes(int64_t C, int math, int split);
 
 /* ------------------------------------------------------------------ a4
  * scale[r, j] = round_to(out_dtype, (2/maxq) * max|W[r, j*g:(j+1)*g]| + 1e-12), kept as fp32.

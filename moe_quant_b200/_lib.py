@@ -52,6 +52,7 @@ SIGNATURES = {
                               c_void_p, c_size_t, c_void_p]),
     "mq_chol_unit_factor": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p, c_size_t,
                                     c_void_p]),
+    "mq_chol_unit_factor_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "mq_gptq_sweep_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int]),
     "mq_quantize_layer": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                   c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,

@@ -20,6 +20,7 @@ void set_error(const char* fmt, ...) {
 // defined in the other translation units
 int launch_to_fp32(const void* src, int dtype, float* dst, int64_t n, cudaStream_t st);
 size_t hinv_workspace_bytes(int64_t C, int math, int split);
+size_t factor_workspace_bytes(int64_t C, int math, int split);
 int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float* diag_out, int math, int split, mq_layer_flags* flags,
                Workspace& ws, cudaStream_t st);
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split);
@@ -120,7 +121,7 @@ extern "C" size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64
                                                     int split_sweep) {
   using namespace mq;
   if (n_tied <= 0 || R <= 0 || C <= 0) return 0;
-  size_t a = engine_workspace_bytes(C, C, 128, math, split_hinv);   // factorisation: rank-128 updates
+  size_t a = factor_workspace_bytes(C, math, split_hinv);            // factorisation: the planes of a super-panel
   size_t b = sweep_workspace_bytes(R, C, math, split_sweep);
   return layer_fixed_bytes(n_tied, R, C) + (a > b ? a : b);
 }

@@ -29,6 +29,10 @@ struct GemmDesc {
   // Ragged last batch: batch b sees N_b = min(N, n_total - b * n_step) columns and, when
   // k_follows_n is set, K_b = N_b as well (the D^-1 factor of a triangular merge).
   int n_total = 0, n_step = 0, k_follows_n = 0;
+  // Tensor path, beta == 1, K > k_round > 0 (a multiple of 64): the partial sums of every k_round
+  // columns of k are added to C one after the other in round-to-nearest fp32, as separate
+  // updates of depth k_round would, instead of meeting inside the tensor core's accumulator.
+  int k_round = 0;
 };
 
 // fp32 CUDA-core implementation; in_dtype is the element type of A and B.

@@ -28,6 +28,8 @@ namespace mq {
 namespace {
 
 constexpr int NB = 128;  // panel width
+constexpr int SUPER_PANELS = 4;               // panels whose far update is applied together
+constexpr int SUPER_NB = SUPER_PANELS * NB;   // 512
 
 // ------------------------------------------------------------------ diagonal block
 // D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
@@ -221,7 +223,8 @@ template <bool IDENTITY>
 __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict__ tblk, int64_t ldt, int64_t t_bs,
                                                         float* __restrict__ rows, int64_t ldr, int64_t r_bs,
                                                         int nrows, int nb_full, int n_total,
-                                                        uint16_t* __restrict__ planes, int64_t plane_stride, int n_planes) {
+                                                        uint16_t* __restrict__ planes, int64_t plane_stride, int n_planes,
+                                                        int plane_ld) {
   extern __shared__ __align__(16) float smem[];
   float* TT = smem;                // [NB][TT_LD], TT[k][j] = T[j][k] for j < k, else 0
   float* dg = smem + NB * TT_LD;   // [NB] diagonal of T
@@ -363,7 +366,7 @@ __global__ void __launch_bounds__(256) trsm_rows_kernel(const float* __restrict_
         uint16_t hi[4], mi[4], lo[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) split_bf16x3(lane * 4 < nb ? a[h][q] : 0.0f, hi[q], mi[q], lo[q]);
-        uint16_t* dst = planes + (int64_t)r * NB + lane * 4;
+        uint16_t* dst = planes + (int64_t)r * plane_ld + lane * 4;   // `planes` already points at this panel's k window
         *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)hi[0] | ((uint32_t)hi[1] << 16), (uint32_t)hi[2] | ((uint32_t)hi[3] << 16));
         if (n_planes > 1)
           *reinterpret_cast<uint2*>(dst + plane_stride) =
@@ -453,10 +456,15 @@ int configure_once() {
 
 }  // namespace
 
+size_t factor_workspace_bytes(int64_t C, int math, int split) {
+  return math == MQ_MATH_TENSOR ? plane_set_bytes(C, SUPER_NB, split) : 0;
+}
+
 size_t hinv_workspace_bytes(int64_t C, int math, int split) {
   size_t bytes = align_up((size_t)C * sizeof(float), 256);          // diag
   bytes += align_up((size_t)C * (size_t)C * sizeof(float), 256);    // merge scratch
-  bytes += engine_workspace_bytes(C, C, C, math, split);
+  size_t a = engine_workspace_bytes(C, C, C, math, split), b = factor_workspace_bytes(C, math, split);
+  bytes += a > b ? a : b;
   return bytes;
 }
 
@@ -475,17 +483,27 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
   const bool tensor = math == MQ_MATH_TENSOR;
   if (tensor) MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "factorisation: split must be 1, 2 or 3 (got %d)", split);
   {
-    // ---- right-looking loop, last panel first
+    // ---- right-looking in two levels, last panel first.  Four panels form a super-panel of 512
+    // columns.  Behind each panel only the columns of its own super-panel that are still to be
+    // factored take their rank-128 update at once (a strip at most 384 wide); everything in
+    // front of the super-panel is updated once per super-panel, with all 512 columns of it in one
+    // contraction, so a tile of the trailing matrix is read and written once per 512 instead of
+    // once per 128 eliminated columns.  Tensor path: the panel solve writes its result as bf16
+    // planes too (k window of its panel inside a 512-wide plane buffer), and the updates read one
+    // plane set as both operands.
     PlaneSet pset;
     if (tensor) {
       Workspace mine = eng.ws;
-      pset.base = mine.take<uint16_t>(plane_set_bytes(C, NB, split) / 2);
+      pset.base = mine.take<uint16_t>(plane_set_bytes(C, SUPER_NB, split) / 2);
       MQ_REQUIRE(pset.base, MQ_ERR_WORKSPACE, "factorisation: workspace too small for the panel planes");
-      pset.planes = split; pset.rows_pad = (int)pad_rows(C); pset.total_rows = pset.rows_pad; pset.K_pad = NB;
+      pset.planes = split; pset.rows_pad = (int)pad_rows(C); pset.total_rows = pset.rows_pad; pset.K_pad = SUPER_NB;
     }
     for (int p = P - 1; p >= 0; --p) {
+      const int p_lo = (p / SUPER_PANELS) * SUPER_PANELS;      // first (lowest) panel of this super-panel
+      const int64_t k0 = (int64_t)p_lo * NB;                   // first column of the super-panel
       const int64_t k1 = (int64_t)p * NB;
       const int nb = (int)((C - k1) < NB ? (C - k1) : NB);
+      const int kwin = (p - p_lo) * NB;                        // this panel's k window in the plane buffer
       float* dblk = H + k1 * ldh + k1;
       {
         ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
@@ -497,20 +515,41 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
       {
         ProfScope prof(PROF_TRSM, (double)k1 * nb * nb, 0.0, st);
         MQ_CUDA(launch_chained(true, trsm_rows_kernel<false>, dim3(grid, 1), dim3(256), kTrsmSmem, st, dblk, ldh, 0, H + k1, ldh, 0,
-                               (int)k1, nb, 0, tensor ? pset.base : nullptr, tensor ? pset.total_rows * NB : 0, split));
+                               (int)k1, nb, 0, tensor ? pset.base + kwin : nullptr, tensor ? pset.total_rows * (int64_t)SUPER_NB : 0,
+                               split, SUPER_NB));
       }
       MQ_LAUNCH_CHECK();
-      GemmDesc g;
-      g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;
-      g.B = H + k1; g.b_rs = 1; g.b_cs = ldh;
-      g.C = H; g.ldc = ldh;
-      g.M = (int)k1; g.N = (int)k1; g.K = nb;
-      g.alpha = -1.0f; g.beta = 1.0f;
-      g.upper_tiles_only = 1;
-      if (tensor) {
-        MQ_TRY(gemm_tensor_planes(g, pset, pset, st));
-      } else {
+      if (!tensor) {
+        GemmDesc g;
+        g.A = H + k1; g.a_rs = ldh; g.a_cs = 1;
+        g.B = H + k1; g.b_rs = 1; g.b_cs = ldh;
+        g.C = H; g.ldc = ldh;
+        g.M = (int)k1; g.N = (int)k1; g.K = nb;
+        g.alpha = -1.0f; g.beta = 1.0f;
+        g.upper_tiles_only = 1;
         MQ_TRY(eng.gemm(g));
+        continue;
+      }
+      if (p > p_lo) {
+        // near: H[0:k1, k0:k1] -= P P[k0:k1]^T, the rest of this super-panel
+        GemmDesc g;
+        g.C = H + k0; g.ldc = ldh;
+        g.M = (int)k1; g.N = (int)(k1 - k0); g.K = nb;
+        g.alpha = -1.0f; g.beta = 1.0f;
+        PlaneSet a = pset, b = pset;
+        a.k0 = kwin;
+        b.k0 = kwin; b.row0 = k0;
+        MQ_TRY(gemm_tensor_planes(g, a, b, st));
+      } else if (k0 > 0) {
+        // far: H[0:k0, 0:k0] -= P_S P_S^T over all columns of the super-panel, tiles on and above the diagonal
+        const int p_hi = (p_lo + SUPER_PANELS - 1) < (P - 1) ? (p_lo + SUPER_PANELS - 1) : (P - 1);
+        GemmDesc g;
+        g.C = H; g.ldc = ldh;
+        g.M = (int)k0; g.N = (int)k0; g.K = (p_hi - p_lo + 1) * NB;
+        g.alpha = -1.0f; g.beta = 1.0f;
+        g.upper_tiles_only = 1;
+        g.k_round = NB;   // partial sums per panel meet in round-to-nearest adds, as in a one-level loop
+        MQ_TRY(gemm_tensor_planes(g, pset, pset, st));
       }
     }
   }
@@ -540,7 +579,7 @@ int hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int64_t ldu, float
   // ---- inverse of the unit factor: invert the diagonal blocks, then merge pairs of blocks
   MQ_CUDA(cudaMemsetAsync(Uhat, 0, (size_t)C * ldu * sizeof(float), st));
   trsm_rows_kernel<true><<<dim3(4, P), 256, kTrsmSmem, st>>>(H, ldh, (int64_t)NB * (ldh + 1), Uhat, ldu,
-                                                             (int64_t)NB * (ldu + 1), NB, NB, (int)C, nullptr, 0, 0);
+                                                             (int64_t)NB * (ldu + 1), NB, NB, (int)C, nullptr, 0, 0, NB);
   MQ_LAUNCH_CHECK();
   for (int64_t s = NB; s < C; s *= 2) {
     const int batch = (int)ceil_div(C - s, 2 * s);
@@ -587,6 +626,11 @@ extern "C" int mq_hinv_upper(float* H, int64_t C, int64_t ldh, float* Uhat, int6
   MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_hinv_upper: bad math %d", math);
   Workspace ws(workspace, workspace_bytes);
   return hinv_upper(H, C, ldh, Uhat, ldu, diag_out, math, split, flags, ws, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t mq_chol_unit_factor_workspace_bytes(int64_t C, int math, int split) {
+  if (C <= 0) return 0;
+  return mq::align_up((size_t)C * sizeof(float), 256) + mq::factor_workspace_bytes(C, math, split);
 }
 
 extern "C" int mq_chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag_out, int math, int split,

@@ -34,6 +34,11 @@ constexpr int ROWS_PER_CTA = SWEEP_THREADS / ROW_LANES;  // 16
 constexpr int U_LANE_LD = LANE_COLS + 4;
 constexpr int U_ROW_LD = ROW_LANES * U_LANE_LD;          // 160 floats
 constexpr size_t kSweepSmem = (size_t)TILE * U_ROW_LD * sizeof(float);
+// Four tiles form a super-block of 512 columns.  Behind each tile only the rest of its own
+// super-block takes the rank-128 update at once; the columns behind the super-block are updated
+// once per super-block with all 512 errors of a row in one contraction, so a tile of W is read
+// and written once per 512 instead of once per 128 swept columns.
+constexpr int SUPER = 4 * TILE;
 
 // One 128 x 128 tile of the factor (top-left element at `src`) -> shared memory in the chunked
 // row layout, strict upper triangle only.  stage: issue the copies (asynchronous 16-byte copies,
@@ -80,6 +85,7 @@ struct SweepArgs {
   int i1, nb;
   const float* Worig; int64_t ldwo;
   uint16_t* err_planes; int64_t plane_stride; int n_planes;
+  int err_ld;   // row stride of err / err_planes (both already point at this tile's k window)
   int bits;
 };
 
@@ -237,7 +243,7 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
           mp[t >> 1] = (uint32_t)m0 | ((uint32_t)m1 << 16);
           lp[t >> 1] = (uint32_t)l0 | ((uint32_t)l1 << 16);
         }
-        uint16_t* dst = a.err_planes + (int64_t)r * TILE + c_local;
+        uint16_t* dst = a.err_planes + (int64_t)r * a.err_ld + c_local;
         reinterpret_cast<uint4*>(dst)[0] = make_uint4(hp[0], hp[1], hp[2], hp[3]);
         reinterpret_cast<uint4*>(dst)[1] = make_uint4(hp[4], hp[5], hp[6], hp[7]);
         if (a.n_planes > 1) {
@@ -249,7 +255,7 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
           reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[1] = make_uint4(lp[4], lp[5], lp[6], lp[7]);
         }
       } else {
-        float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * TILE + c_local);
+        float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * a.err_ld + c_local);
 #pragma unroll
         for (int qd = 0; qd < LANE_COLS / 4; ++qd) dst[qd] = make_float4(e[4 * qd], e[4 * qd + 1], e[4 * qd + 2], e[4 * qd + 3]);
       }
@@ -287,9 +293,8 @@ int configure_once() {
 }  // namespace
 
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
-  size_t bytes = align_up((size_t)R * TILE * sizeof(float), 256);
-  if (math == MQ_MATH_TENSOR) bytes += plane_set_bytes(R, TILE, split) + plane_set_bytes(C, C, split);
-  return bytes;
+  if (math == MQ_MATH_TENSOR) return plane_set_bytes(R, SUPER, split) + plane_set_bytes(C, C, split);
+  return align_up((size_t)R * TILE * sizeof(float), 256);
 }
 
 int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, int64_t ldu, const float* scale,
@@ -300,21 +305,21 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   // columns were divided by col_div; the plane split divides where it reads it.  The diagonal
   // blocks, which the tiles read, are already scaled.
   MQ_TRY(configure_once());
-  float* err = ws.take<float>((size_t)R * TILE);
-  MQ_REQUIRE(err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
+  const bool tensor = math == MQ_MATH_TENSOR;
+  float* err = tensor ? nullptr : ws.take<float>((size_t)R * TILE);
+  MQ_REQUIRE(tensor || err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
   Engine eng(math, split, ws, st);
   // Tensor path: the factor is cut into transposed planes once (row n, k -> U[k][n]); the lazy
   // update of tile i1 then reads the window k in [i1, i1+128), rows n >= i2 of those planes,
   // and the sweep kernel writes its errors as planes itself.  No per-tile conversion passes.
   PlaneSet err_set, u_set;
-  const bool tensor = math == MQ_MATH_TENSOR;
   if (tensor) {
     MQ_REQUIRE(split >= 1 && split <= 3, MQ_ERR_ARGUMENT, "mq_gptq_sweep: split must be 1, 2 or 3 (got %d)", split);
-    uint16_t* ep = ws.take<uint16_t>(plane_set_bytes(R, TILE, split) / 2);
+    uint16_t* ep = ws.take<uint16_t>(plane_set_bytes(R, SUPER, split) / 2);
     uint16_t* up = ws.take<uint16_t>(plane_set_bytes(C, C, split) / 2);
     MQ_REQUIRE(ep && up, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small for the operand planes");
     err_set.base = ep; err_set.planes = split; err_set.rows_pad = (int)pad_rows(R); err_set.total_rows = err_set.rows_pad;
-    err_set.K_pad = TILE;
+    err_set.K_pad = SUPER;
     // the lazy updates read Uhat[i1:i2, i2:]: only blocks strictly above the diagonal
     MQ_TRY(make_planes_f32(Uhat, 1, ldu, (int)C, (int)C, split, up, &u_set, st, true, col_div));
   }
@@ -328,9 +333,10 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   sa.packed = packed;
   sa.deq = deq; sa.err = err;
   sa.Worig = Worig; sa.ldwo = ldwo;
-  sa.err_planes = tensor ? err_set.base : nullptr;
-  sa.plane_stride = tensor ? err_set.total_rows * (int64_t)TILE : 0;
+  sa.err_planes = nullptr;
+  sa.plane_stride = tensor ? err_set.total_rows * (int64_t)SUPER : 0;
   sa.n_planes = split;
+  sa.err_ld = tensor ? SUPER : TILE;
   sa.bits = bits;
   const bool uniform = group % LANE_COLS == 0;
   // every CTA stages the tile of the factor once and then walks row groups: no more CTAs than
@@ -346,6 +352,7 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       // bytes the tile must move: W in, codes out, errors out, the triangle of Uhat once
       ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
       sa.i1 = (int)i1; sa.nb = nb;
+      if (tensor) sa.err_planes = err_set.base + (i1 % SUPER);
       switch (out_dtype) {
         case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
         case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
@@ -354,21 +361,38 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
     }
     MQ_LAUNCH_CHECK();
     const int64_t i2 = i1 + nb;
-    if (i2 < C) {
+    if (i2 >= C) break;
+    if (!tensor) {
       GemmDesc g;
       g.A = err; g.a_rs = TILE; g.a_cs = 1;
       g.B = Uhat + i1 * ldu + i2; g.b_rs = ldu; g.b_cs = 1;
       g.C = W + i2; g.ldc = ldw;
       g.M = (int)R; g.N = (int)(C - i2); g.K = nb;
       g.alpha = 1.0f; g.beta = 1.0f;
-      if (tensor) {
-        PlaneSet b = u_set;
-        b.row0 = i2;
-        b.k0 = (int)i1;
-        MQ_TRY(gemm_tensor_planes(g, err_set, b, st));
-      } else {
-        MQ_TRY(eng.gemm(g));
-      }
+      MQ_TRY(eng.gemm(g));
+      continue;
+    }
+    const int64_t s0 = i1 / SUPER * SUPER;                        // first column of this super-block
+    const int64_t s1 = (s0 + SUPER) < C ? (s0 + SUPER) : C;       // one past its last column
+    if (i2 < s1) {
+      // near: W[:, i2:s1] += E_tile Uhat[i1:i2, i2:s1]
+      GemmDesc g;
+      g.C = W + i2; g.ldc = ldw;
+      g.M = (int)R; g.N = (int)(s1 - i2); g.K = nb;
+      g.alpha = 1.0f; g.beta = 1.0f;
+      PlaneSet a = err_set, b = u_set;
+      a.k0 = (int)(i1 - s0);
+      b.row0 = i2; b.k0 = (int)i1;
+      MQ_TRY(gemm_tensor_planes(g, a, b, st));
+    } else {
+      // far: W[:, s1:] += E_super Uhat[s0:s1, s1:], all errors of the super-block in one contraction
+      GemmDesc g;
+      g.C = W + s1; g.ldc = ldw;
+      g.M = (int)R; g.N = (int)(C - s1); g.K = (int)(s1 - s0);
+      g.alpha = 1.0f; g.beta = 1.0f;
+      PlaneSet b = u_set;
+      b.row0 = s1; b.k0 = (int)s0;
+      MQ_TRY(gemm_tensor_planes(g, err_set, b, st));
     }
   }
   return MQ_OK;

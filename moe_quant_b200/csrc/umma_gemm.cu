@@ -53,6 +53,7 @@ struct UmmaParams {
   uint32_t idesc;
   int mirror;  // symmetric result: every block above the diagonal is also stored transposed
   int c_tma;   // panel kernel epilogue: 0 = loads/stores by the warps, 1 = TMA store (beta == 0), 2 = TMA add (beta == 1)
+  int drain_slabs;  // streaming kernel: slabs of k per accumulator before it is added to C (0 = all of K)
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -112,6 +113,7 @@ __device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, uint32_t src,
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
@@ -870,6 +872,219 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) umma_panel_kernel(const __gri
   }
 }
 
+// ---------------------------------------------------------------- K > 128 with several planes: persistent streaming GEMM
+// The far updates of the two-level factorisation and sweep: 512 of k at a time on a large fp32
+// matrix, three planes per operand.  One CTA per SM walks the list of kept output tiles (tile
+// number blockIdx.x + i * gridDim.x).  Both operands stream through a ring of two stages, each
+// one 64-wide slab of k of A and of B (all planes: 96 KB with three), which keeps running across
+// tiles; the accumulators alternate between two TMEM tiles, and the epilogue of tile i (C through
+// the TMA unit where that is possible) runs under the MMAs of tile i + 1.  With one tile per CTA
+// the tensor pipe idled through every prologue and epilogue (a quarter of a 512-deep tile).
+//
+// drain_slabs > 0 (with the TMA add only): the accumulator is handed to the epilogue after every
+// drain_slabs slabs of k and added to C there, so the partial sums of K meet in round-to-nearest
+// fp32 adds exactly as if the update had been issued as separate rank-128 updates.  The tensor
+// core's own accumulation truncates; over 512 of k that bias is four times the one of 128, which
+// the factorisation of an ill-conditioned Hessian does not forgive.  The adds of one tile still
+// hit the L2 only: the tile is fetched from and written back to HBM once.
+struct TileWalk {
+  int m, n;
+  __device__ __forceinline__ void seek(int idx, int n_tiles, int upper) {
+    if (!upper) { m = idx / n_tiles; n = idx - m * n_tiles; return; }
+    m = 0;
+    for (;;) {                       // row m of the triangle keeps n_tiles - m tiles
+      const int cnt = n_tiles - m;
+      if (idx < cnt) { n = m + idx; return; }
+      idx -= cnt;
+      ++m;
+    }
+  }
+};
+
+// Unit u of a CTA's work: one accumulator's worth, `per_drain` slabs of k of one tile; the units
+// of a tile follow one another.  (Letting two tiles take turns, so that the wait for the previous
+// adds to a tile has a unit of slack, measured slower.)
+struct UnitWalk {
+  int tile, s0;
+  __device__ __forceinline__ void seek(int u, int n_drains, int per_drain) {
+    tile = u / n_drains;
+    s0 = (u - tile * n_drains) * per_drain;
+  }
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1) umma_stream_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                   const __grid_constant__ CUtensorMap map_b,
+                                                                   const __grid_constant__ CUtensorMap map_c,
+                                                                   const UmmaParams p, const int total) {
+  const int n_tiles = (p.N + TILE_N - 1) / TILE_N;
+  const int my_tiles = ((int)blockIdx.x < total) ? (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  if (my_tiles == 0) return;
+  const int n_slabs = (p.K + SLAB_K - 1) / SLAB_K;
+  const int per_drain = (p.drain_slabs > 0 && p.drain_slabs < n_slabs) ? p.drain_slabs : n_slabs;
+  const int n_drains = (n_slabs + per_drain - 1) / per_drain;
+  const int n_units = my_tiles * n_drains;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int planes = p.planes;
+  const uint32_t stage_bytes = 2u * (uint32_t)planes * PLANE_TILE_BYTES;
+  __shared__ __align__(8) uint64_t bars[8];
+  __shared__ uint32_t tmem_slot;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[2]);
+  const uint32_t acc_full = smem_u32(&bars[4]), acc_empty = smem_u32(&bars[6]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t idesc = p.idesc;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+      mbar_init(acc_full + 8 * s, 1);
+      mbar_init(acc_empty + 8 * s, 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const uint32_t small_off = planes > 1 ? (uint32_t)TILE_N : 0u;
+  const uint32_t acc_stride = planes > 1 ? 2u * TILE_N : (uint32_t)TILE_N;
+  const uint32_t tmem_cols = 2u * acc_stride;
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+  chain_wait();
+  chain_release();
+
+  if (warp == 0) {
+    int it = 0;
+    bool ok = true;
+    for (int u = 0; u < n_units && ok; ++u) {
+      UnitWalk uw;
+      uw.seek(u, n_drains, per_drain);
+      TileWalk w;
+      w.seek((int)blockIdx.x + uw.tile * (int)gridDim.x, n_tiles, p.upper_tiles_only);
+      const int a_row = w.m * TILE_M + p.a_row0, b_row = w.n * TILE_N + p.b_row0;
+      const int s1 = (uw.s0 + per_drain) < n_slabs ? (uw.s0 + per_drain) : n_slabs;
+      for (int s = uw.s0; s < s1; ++s, ++it) {
+        const int st = it & 1;
+        if (it >= 2 && !mbar_wait(empty0 + 8 * st, ((it >> 1) - 1) & 1, 41)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(full0 + 8 * st, stage_bytes);
+          const uint32_t dst = smem_base + (uint32_t)st * stage_bytes;
+          for (int pl = 0; pl < planes; ++pl) {
+            tma_load_3d(dst + (uint32_t)pl * PLANE_TILE_BYTES, &map_a, full0 + 8 * st, s * SLAB_K + p.a_k0, a_row, pl);
+            tma_load_3d(dst + (uint32_t)(planes + pl) * PLANE_TILE_BYTES, &map_b, full0 + 8 * st, s * SLAB_K + p.b_k0, b_row, pl);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    int it = 0;
+    bool ok = true;
+    for (int u = 0; u < n_units && ok; ++u) {   // one accumulator handed to the epilogue per unit
+      UnitWalk uw;
+      uw.seek(u, n_drains, per_drain);
+      const int acc = u & 1;
+      if (u >= 2) ok = mbar_wait(acc_empty + 8 * acc, ((u >> 1) - 1) & 1, 42);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t accumulate = 0, accumulate_small = 0;
+      const int s1 = (uw.s0 + per_drain) < n_slabs ? (uw.s0 + per_drain) : n_slabs;
+      for (int s = uw.s0; s < s1 && ok; ++s, ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(full0 + 8 * st, (it >> 1) & 1, 43);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
+          const uint32_t b_tile = a_tile + (uint32_t)planes * PLANE_TILE_BYTES;
+          issue_slab_any(planes, tmem_acc + (uint32_t)acc * acc_stride, small_off, a_tile, b_tile, idesc, accumulate, accumulate_small);
+          umma_commit(empty0 + 8 * st);  // the stage is free once these MMAs have read it
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(acc_full + 8 * acc);
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    bool ok = true;
+    if (p.c_tma) {
+      // Each warp owns two 4 KB boxes (32 rows x 128 B, 128-byte swizzle) behind the operand ring.
+      const uint32_t box0 = smem_base + 2u * stage_bytes + (uint32_t)(warp - 2) * 8192u;
+      const uint32_t my_row = box0 + (uint32_t)lane * 128u;
+      int chunk = 0;
+      for (int u = 0; u < n_units && ok; ++u) {
+        UnitWalk uw;
+        uw.seek(u, n_drains, per_drain);
+        TileWalk w;
+        w.seek((int)blockIdx.x + uw.tile * (int)gridDim.x, n_tiles, p.upper_tiles_only);
+        const int n0 = w.n * TILE_N;
+        const int y = w.m * TILE_M + q * 32;
+        const int acc = u & 1;
+        ok = mbar_wait(acc_full + 8 * acc, (u >> 1) & 1, 44);
+        if (!ok) break;
+        tc_fence_after();
+        if (uw.s0 > 0) {
+          // the adds of the previous part of this tile are done before this part's are issued:
+          // every element receives its partial sums in the order of k, run after run
+          if (lane == 0) bulk_wait_all();
+          __syncwarp();
+        }
+#pragma unroll 1
+        for (int c = 0; c < TILE_N / 32; ++c, ++chunk) {
+          float v[32];
+          tmem_ld32_sum(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * acc_stride + (uint32_t)(c * 32), small_off, v);
+          if (c == TILE_N / 32 - 1) {
+            // the accumulator is in registers: hand its TMEM columns back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+          }
+          if (lane == 0) bulk_wait_read_1();
+          __syncwarp();
+          const uint32_t dst = my_row + (uint32_t)(chunk & 1) * 4096u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((j ^ (lane & 7)) << 4)),
+                         "f"(p.alpha * v[4 * j]), "f"(p.alpha * v[4 * j + 1]), "f"(p.alpha * v[4 * j + 2]),
+                         "f"(p.alpha * v[4 * j + 3])
+                         : "memory");
+          fence_async_smem();
+          __syncwarp();
+          const int x = n0 + c * 32;
+          if (lane == 0 && y < p.M && x < p.N) {
+            if (p.c_tma == 2) tma_add_2d(&map_c, box0 + (uint32_t)(chunk & 1) * 4096u, x, y);
+            else tma_store_2d(&map_c, box0 + (uint32_t)(chunk & 1) * 4096u, x, y);
+          }
+          if (lane == 0) bulk_commit();
+        }
+      }
+      if (lane == 0) bulk_wait_read_all();  // the boxes have left shared memory; the writes land before the grid completes
+      __syncwarp();
+    } else {
+      float* stage_base = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + 2u * stage_bytes);
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int acc = i & 1;
+        TileWalk w;
+        w.seek((int)blockIdx.x + i * (int)gridDim.x, n_tiles, p.upper_tiles_only);
+        ok = epilogue_tile<TILE_N>(p.alpha, p.beta, p.ldc, p.M, 0, p.C, w.m * TILE_M, w.n * TILE_N, p.N,
+                                   tmem_acc + (uint32_t)acc * acc_stride, stage_base, warp, lane, n_slabs > 0, acc_full + 8 * acc,
+                                   (uint32_t)((i >> 1) & 1), small_off);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, tmem_cols);
+  }
+}
+
 // ---------------------------------------------------------------- operand planes
 // dst plane pl, batch b, row r, k  <-  piece pl of src[b][r][k]; zero outside the logical
 // (rows_b x K_b) extent up to the padded (rows_pad x K_pad) one.  32 x 32 tiles; when the
@@ -1136,6 +1351,7 @@ int configure_once() {
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
     MQ_CUDA(cudaFuncSetAttribute(umma_gemm_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
     MQ_CUDA(cudaFuncSetAttribute(umma_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    MQ_CUDA(cudaFuncSetAttribute(umma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     done[dev & 63] = true;
   }
   return MQ_OK;
@@ -1156,6 +1372,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   p.a_rows_pad = A.rows_pad; p.b_rows_pad = B.rows_pad;
   p.a_row0 = (int)A.row0; p.a_k0 = A.k0; p.b_row0 = (int)B.row0; p.b_k0 = B.k0;
   p.planes = A.planes;
+  p.drain_slabs = 0;
   p.nterms = 0;
   for (int i = 0; i < A.planes; ++i)
     for (int j = 0; i + j < A.planes; ++j) ++p.nterms;
@@ -1207,6 +1424,26 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
     const size_t staging = p.c_tma ? (size_t)4 * 2 * 4096 : (size_t)STAGE_BYTES;
     const size_t psmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + staging;  // A: two slabs, B: two stages, staging
     MQ_CUDA(launch_chained(true, umma_panel_kernel, pgrid, dim3(GEMM_THREADS), psmem, st, map_a, map_b, map_c, p, run));
+  } else if (A.planes > 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && !d.mirror_to_lower && d.K > 2 * SLAB_K) {
+    // deep update with several planes: persistent streaming kernel
+    const int m_tiles = (int)ceil_div(d.M, TILE_M), n_tiles = (int)ceil_div(d.N, TILE_N);
+    long long tiles = (long long)m_tiles * n_tiles;
+    if (d.upper_tiles_only) {
+      const int rows = m_tiles < n_tiles ? m_tiles : n_tiles;   // row m keeps n_tiles - m tiles
+      tiles = (long long)rows * n_tiles - (long long)rows * (rows - 1) / 2;
+    }
+    CUtensorMap map_c;
+    memset(&map_c, 0, sizeof(map_c));
+    p.c_tma = 0;
+    if ((d.ldc & 3) == 0 && (d.N & 3) == 0 && (reinterpret_cast<uintptr_t>(d.C) & 15) == 0 && (d.beta == 0.0f || d.beta == 1.0f)) {
+      MQ_TRY(encode_c_map(d.C, d.ldc, d.M, d.N, &map_c));
+      p.c_tma = d.beta == 0.0f ? 1 : 2;
+    }
+    p.drain_slabs = (d.k_round > 0 && p.c_tma == 2) ? d.k_round / SLAB_K : 0;
+    const size_t staging = p.c_tma ? (size_t)4 * 2 * 4096 : (size_t)STAGE_BYTES;
+    const size_t ssmem = (size_t)4 * A.planes * PLANE_TILE_BYTES + 1024 + staging;   // two stages of A and B slabs, staging
+    MQ_CUDA(launch_chained(true, umma_stream_kernel, dim3((unsigned)(tiles < 148 ? tiles : 148)), dim3(GEMM_THREADS), ssmem, st,
+                           map_a, map_b, map_c, p, (int)tiles));
   } else {
     if (A.planes == 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.N >= 256) {
       // one product per element: 128 x 256 tiles, four 48 KB stages, one persistent CTA per SM
@@ -1234,6 +1471,24 @@ int gemm_tensor_planes(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, 
   if (d.M <= 0 || d.N <= 0 || d.batch <= 0) return MQ_OK;
   MQ_REQUIRE(A.planes == B.planes && A.planes >= 1 && A.planes <= 3 && A.fp16 == B.fp16, MQ_ERR_ARGUMENT,
              "tensor engine: operand plane sets do not match");
+  if (d.k_round > 0 && d.K > d.k_round) {
+    MQ_REQUIRE(d.k_round % SLAB_K == 0 && d.beta == 1.0f && d.batch == 1, MQ_ERR_ARGUMENT,
+               "tensor engine: k_round needs a multiple of %d, beta == 1 and one batch", SLAB_K);
+    const bool c_tma = (d.ldc & 3) == 0 && (d.N & 3) == 0 && (reinterpret_cast<uintptr_t>(d.C) & 15) == 0;
+    if (!c_tma || A.planes == 1) {
+      // no add at the L2 for this C (or one plane, which the streaming kernel does not take):
+      // the same partial sums as separate updates
+      for (int k = 0; k < d.K; k += d.k_round) {
+        GemmDesc part = d;
+        part.K = (d.K - k) < d.k_round ? (d.K - k) : d.k_round;
+        part.k_round = 0;
+        PlaneSet a = A, b = B;
+        a.k0 += k; b.k0 += k;
+        MQ_TRY(launch_umma(part, a, b, st));
+      }
+      return MQ_OK;
+    }
+  }
   return launch_umma(d, A, B, st);
 }
 

@@ -179,7 +179,7 @@ def chol_unit_factor(H: Tensor, precision: Optional[Precision] = None, flags: Op
     diag = torch.empty(C, dtype=torch.float32, device=H.device)
     if flags is None:
         flags = _flags_tensor(H.device)
-    nbytes = L.mq_gemm_workspace_bytes(C, C, 128, p.math, p.split_hinv) + 4 * C + 512
+    nbytes = L.mq_chol_unit_factor_workspace_bytes(C, p.math, p.split_hinv)
     ws = _lib.workspace(H.device, nbytes)
     with torch.cuda.device(H.device):
         check(L.mq_chol_unit_factor(ptr(H), C, H.stride(0), ptr(diag), p.math, p.split_hinv, ptr(flags), ptr(ws),

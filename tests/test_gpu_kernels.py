@@ -332,13 +332,18 @@ def test_gemm_engine_upper_tiles_only(cuda, precision):
 
 @pytest.mark.parametrize("beta", [0.0, 1.0, 0.5])
 @pytest.mark.parametrize("upper,N", [(False, 2780), (False, 2777), (True, 3304)])
-def test_gemm_engine_rank128_update_many_tiles(cuda, beta, upper, N):
+@pytest.mark.parametrize("deep", [False, True])
+def test_gemm_engine_rank128_update_many_tiles(cuda, beta, upper, N, deep):
     """Rank-128 updates with at least two tiles per SM leave through the TMA unit (store for
     beta 0, add at the L2 for beta 1); any other beta, or fewer tiles, goes through the warps'
     own loads and stores, and so does an N that is not a multiple of 4.  Ragged edges (M, N not
     multiples of the 32-wide boxes) and a C that is a window of a wider matrix must not touch
-    anything outside the window."""
+    anything outside the window.  `deep`: the same with 512 (and a ragged 300) contraction
+    columns, the persistent streaming kernel that the two-level updates of the factorisation
+    and of the sweep use."""
     M, K = (N, 128) if upper else (2500, 100)
+    if deep:
+        K = 512 if upper else 300
     g = torch.Generator().manual_seed(11)
     A, B = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
     if upper:

@@ -117,3 +117,46 @@ def test_engine_handle_equals_the_reference_handle_on_the_device(cuda, name):
     q, s, _z = h.quantize(4)
     assert torch.equal(s.cpu().float(), scale)
     assert O.code_agreement(q.cpu(), _t(f"{name}.qweight")) >= 0.995
+
+
+# ---------------------------------------------------------------------------- the MSE scale search
+MSE_CASES = ["mse_bfloat16_g128", "mse_float16_g32", "mse_float32_g64"]
+
+
+def _mse_inputs(name):
+    meta = ast.literal_eval(str(Z[f"{name}.meta"]))
+    dtype = getattr(torch, meta["dtype"])
+    return _t(f"{name}.W", dtype), _t(f"{name}.scale").float(), _t(f"{name}.scale_absmax").float(), meta["g"], dtype
+
+
+def _check_mse_scales(got, want, base, dtype):
+    """The reference sums |.|^2.4 over a group in whatever order its device reduction takes, so a
+    candidate next to the minimum may win in one implementation and lose in another: nearly all
+    scales identical, and every scale one of the hundred candidates of its group."""
+    assert got.shape == want.shape
+    assert float((got == want).float().mean()) >= 0.97
+    cands = O.round_fp(base[..., None] * torch.linspace(1, 0.2, 100), dtype)
+    assert bool((cands == got[..., None]).any(-1).all())
+    assert float(((got - want).abs() / want).max()) <= 0.02    # a neighbour at worst: the grid step is 0.8 %
+
+
+@pytest.mark.parametrize("name", MSE_CASES)
+def test_oracle_mse_scales_equal_the_reference_grid_search(name):
+    """`get_quantization_grid(..., QuantizationScale.MSE)` of the reference, run on the device."""
+    W, want, base, g, dtype = _mse_inputs(name)
+    s0, zero, maxq = O.symmetric_grid(W.float(), g, 4, dtype)
+    assert torch.equal(s0.float(), base)
+    got = O.mse_scale(W.float().unflatten(-1, (-1, g)), s0, zero, maxq, dtype).float()
+    _check_mse_scales(got, want, base, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", MSE_CASES)
+def test_cuda_mse_scales_equal_the_reference_grid_search(cuda, name):
+    from moe_quant_b200 import ops
+    W, want, base, g, dtype = _mse_inputs(name)
+    Wd = W.float().to(cuda)
+    s0 = ops.absmax_scales(Wd, g, 4, dtype)
+    assert torch.equal(s0.cpu().float(), base)
+    got = ops.mse_scales(Wd, s0, g, 4, dtype).cpu().float()
+    _check_mse_scales(got, want, base, dtype)

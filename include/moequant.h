@@ -52,6 +52,13 @@ typedef enum { MQ_F32 = 0, MQ_BF16 = 1, MQ_F16 = 2 } mq_dtype;
  *                   (`split` planes: 1 -> 1 product, 2 -> 3, 3 -> 6).          */
 typedef enum { MQ_MATH_FP32 = 0, MQ_MATH_TENSOR = 1 } mq_math;
 
+/* Flag that may be OR-ed into the `math` argument of mq_gptq_sweep and mq_quantize_layer (and of
+ * their *_workspace_bytes): the caller processes several layers at once on different streams
+ * (gptq.quantize_many).  The library then prefers launch shapes that occupy few SMs over the
+ * lowest latency of a single layer: the sweep's tiles run one weight row per thread on R/64
+ * SMs instead of eight lanes per row on R/16.  Results are bit-identical with and without it. */
+#define MQ_MATH_COMPACT 0x100
+
 /* Device-side status of one layer, written by mq_hessian_prepare / mq_hinv_upper.
  * Mirrors GPTQ.issue_nan_hessian / issue_non_invertible (src/gptq.py:61-63). */
 typedef struct {

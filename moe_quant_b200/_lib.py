@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libmoequant_sm100.so")
 
 MQ_F32, MQ_BF16, MQ_F16 = 0, 1, 2
 MATH_FP32, MATH_TENSOR = 0, 1
+MATH_COMPACT = 0x100   # MQ_MATH_COMPACT: flag OR-ed into the math argument of the sweep / whole-layer calls
 
 _DTYPES = {torch.float32: MQ_F32, torch.bfloat16: MQ_BF16, torch.float16: MQ_F16}
 

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import concurrent.futures
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -37,18 +38,35 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _includes(path: str, dirs, seen=None):
+    """`path` and every file it includes with quotes, recursively (searched in `dirs`): a source
+    is recompiled when one of these is newer than its object.  The row-per-thread sweep kernels
+    take minutes to compile, so a change elsewhere should not rebuild them."""
+    seen = seen if seen is not None else []
+    if path in seen:
+        return seen
+    seen.append(path)
+    with open(path) as f:
+        names = re.findall(r'^\s*#\s*include\s+"([^"]+)"', f.read(), flags=re.M)
+    for name in names:
+        for d in dirs:
+            cand = os.path.join(d, name)
+            if os.path.exists(cand):
+                _includes(cand, dirs, seen)
+                break
+    return seen
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
     objdir = os.path.join(CSRC, "build")
     os.makedirs(objdir, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     inc = os.path.join(os.path.dirname(HERE), "include")
-    headers += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
 
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         path = os.path.join(CSRC, src)
-        if force or _stale(obj, [path] + headers):
+        if force or _stale(obj, _includes(path, (CSRC, inc))):
             cmd = [nvcc, *FLAGS, "-c", path, "-o", obj]
             r = subprocess.run(cmd, capture_output=True, text=True)
             log = os.path.join(objdir, src + ".log")
@@ -60,7 +78,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(r.stderr)
         return obj
 
-    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, len(SOURCES))) as pool:
         objs = list(pool.map(compile_one, SOURCES))
     if force or _stale(OUT, objs):
         cmd = [nvcc, "-shared", "-o", OUT, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]

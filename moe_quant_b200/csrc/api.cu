@@ -121,6 +121,7 @@ extern "C" size_t mq_quantize_layer_workspace_bytes(int n_tied, int64_t R, int64
                                                     int split_sweep) {
   using namespace mq;
   if (n_tied <= 0 || R <= 0 || C <= 0) return 0;
+  math &= ~MQ_MATH_COMPACT;
   size_t a = factor_workspace_bytes(C, math, split_hinv);            // factorisation: the planes of a super-panel
   size_t b = sweep_workspace_bytes(R, C, math, split_sweep);
   return layer_fixed_bytes(n_tied, R, C) + (a > b ? a : b);
@@ -147,6 +148,9 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
     MQ_REQUIRE(!packed || (packed[i] && bits == 4 && aligned(packed[i], 4)), MQ_ERR_UNSUPPORTED,
                "mq_quantize_layer: packed words need bits == 4 and a 4-byte aligned buffer per layer");
   }
+  const int sweep_math = math;   // the sweep honours MQ_MATH_COMPACT
+  math &= ~MQ_MATH_COMPACT;
+  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_quantize_layer: bad math %d", sweep_math);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace ws(workspace, workspace_bytes);
   float* U = ws.take<float>((size_t)C * C);
@@ -189,7 +193,7 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
     MQ_CUDA(cudaMemcpyAsync(Wo[i], Wf[i], (size_t)R * C * sizeof(float), cudaMemcpyDeviceToDevice, st));
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
     MQ_TRY(gptq_sweep(Wf[i], R, C, C, U, C, scale_out[i], nullptr, group, C / group, 1, bits, w_dtype, codes[i],
-                      dequantized ? dequantized[i] : nullptr, Wo[i], C, math, split_sweep, sub, st, unscaled ? diag : nullptr,
+                      dequantized ? dequantized[i] : nullptr, Wo[i], C, sweep_math, split_sweep, sub, st, unscaled ? diag : nullptr,
                       packed ? packed[i] : nullptr));
   }
   return MQ_OK;

@@ -19,16 +19,17 @@
 // result, so the transposes of src/gptq.py:191-199 never happen.
 #include "engine.cuh"
 #include "profile.cuh"
+#include "sweep.cuh"
+#include "sweep_rows.cuh"
 
 namespace mq {
 
 namespace {
 
-constexpr int TILE = 128;
+constexpr int TILE = SWEEP_TILE;
 constexpr int ROW_LANES = 8;                             // lanes that share one weight row
 constexpr int LANE_COLS = TILE / ROW_LANES;              // 16 consecutive columns per lane
-constexpr int SWEEP_THREADS = 128;                       // four warps of four rows
-constexpr int ROWS_PER_CTA = SWEEP_THREADS / ROW_LANES;  // 16
+// THREADS per CTA is a template parameter (128, 256 or 512): THREADS / 8 rows per CTA
 // The tile of the factor in shared memory: row j holds eight chunks of 16 columns, 20 floats
 // apart, so that the eight lanes of a row read their chunks from disjoint groups of banks.
 constexpr int U_LANE_LD = LANE_COLS + 4;
@@ -46,7 +47,7 @@ constexpr int SUPER = 4 * TILE;
 // and past nb); trim: wait for them and zero the entries on and below the diagonal inside each
 // row's diagonal quad.  Every thread of the CTA must call both.
 __device__ __forceinline__ void stage_factor_tile(float* ublk, const float* __restrict__ src, int64_t ldu, int nb) {
-  for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += SWEEP_THREADS) {
+  for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
     const int j = idx >> 5, k4 = (idx & 31) * 4;
     const bool keep = j < nb && k4 < nb && k4 + 3 > j;
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&ublk[j * U_ROW_LD + (k4 >> 4) * U_LANE_LD + (k4 & 15)]);
@@ -59,7 +60,7 @@ __device__ __forceinline__ void stage_factor_tile(float* ublk, const float* __re
 __device__ __forceinline__ void trim_factor_tile(float* ublk, int nb) {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
-  for (int j = threadIdx.x; j < nb; j += SWEEP_THREADS) {
+  for (int j = threadIdx.x; j < nb; j += blockDim.x) {
     const int k4 = j & ~3;
     float* q = &ublk[j * U_ROW_LD + (k4 >> 4) * U_LANE_LD + (k4 & 15)];
     for (int k = 0; k <= (j & 3); ++k) q[k] = 0.0f;
@@ -67,31 +68,10 @@ __device__ __forceinline__ void trim_factor_tile(float* ublk, int nb) {
   __syncthreads();
 }
 
-// eight codes below 16, held as bytes in two words (lowest byte = first column) -> one word of nibbles
-__device__ __forceinline__ uint32_t pack_nibbles(uint32_t lo4, uint32_t hi4) {
-  const uint32_t w = (lo4 & 0xFu) | ((lo4 >> 4) & 0xF0u) | ((lo4 >> 8) & 0xF00u) | ((lo4 >> 12) & 0xF000u);
-  const uint32_t v = (hi4 & 0xFu) | ((hi4 >> 4) & 0xF0u) | ((hi4 >> 8) & 0xF00u) | ((hi4 >> 12) & 0xF000u);
-  return w | (v << 16);
-}
-
-struct SweepArgs {
-  const float* W; int64_t ldw; int R;
-  const float* U; int64_t ldu;
-  const float* scale; const float* zero; int64_t group, s_rs, s_gs;
-  float maxq, zero_default;
-  uint8_t* codes; int64_t C;
-  int32_t* packed;   // optional (R, C/8) int32: the same codes, eight 4-bit nibbles per word
-  void* deq; float* err;
-  int i1, nb;
-  const float* Worig; int64_t ldwo;
-  uint16_t* err_planes; int64_t plane_stride; int n_planes;
-  int err_ld;   // row stride of err / err_planes (both already point at this tile's k window)
-  int bits;
-};
-
 // UNIFORM: the sixteen columns of a lane lie in one quantization group (group % 16 == 0).
-template <int DT, bool UNIFORM>
-__global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepArgs a) {
+template <int DT, bool UNIFORM, int THREADS>
+__global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) {
+  constexpr int ROWS_PER_CTA = THREADS / ROW_LANES;
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][U_ROW_LD], strict upper triangle of the tile, 0 elsewhere
   const int nb = a.nb, i1 = a.i1;
@@ -265,15 +245,15 @@ __global__ void __launch_bounds__(SWEEP_THREADS) sweep_tile_kernel(const SweepAr
 
 template <int DT>
 int launch_sweep_tile(bool chained, bool uniform, int grid, cudaStream_t st, const SweepArgs& args) {
-  if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true>, dim3(grid), dim3(SWEEP_THREADS), kSweepSmem, st, args));
-  else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false>, dim3(grid), dim3(SWEEP_THREADS), kSweepSmem, st, args));
+  if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true, 128>, dim3(grid), dim3(128), kSweepSmem, st, args));
+  else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false, 128>, dim3(grid), dim3(128), kSweepSmem, st, args));
   return MQ_OK;
 }
 
 template <int DT>
 int configure_dtype() {
-  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
-  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
   return MQ_OK;
 }
 
@@ -293,6 +273,7 @@ int configure_once() {
 }  // namespace
 
 size_t sweep_workspace_bytes(int64_t R, int64_t C, int math, int split) {
+  math &= ~MQ_MATH_COMPACT;
   if (math == MQ_MATH_TENSOR) return plane_set_bytes(R, SUPER, split) + plane_set_bytes(C, C, split);
   return align_up((size_t)R * TILE * sizeof(float), 256);
 }
@@ -305,6 +286,8 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   // columns were divided by col_div; the plane split divides where it reads it.  The diagonal
   // blocks, which the tiles read, are already scaled.
   MQ_TRY(configure_once());
+  const bool compact = (math & MQ_MATH_COMPACT) != 0;
+  math &= ~MQ_MATH_COMPACT;
   const bool tensor = math == MQ_MATH_TENSOR;
   float* err = tensor ? nullptr : ws.take<float>((size_t)R * TILE);
   MQ_REQUIRE(tensor || err, MQ_ERR_WORKSPACE, "mq_gptq_sweep: workspace too small");
@@ -341,8 +324,12 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   const bool uniform = group % LANE_COLS == 0;
   // every CTA stages the tile of the factor once and then walks row groups: no more CTAs than
   // two per SM, so that a tall layer does not stage the same tile thousands of times
-  const int64_t row_groups = ceil_div(R, ROWS_PER_CTA);
+  const int64_t row_groups = ceil_div(R, 128 / ROW_LANES);
   const int grid = (int)(row_groups < 2 * 148 ? row_groups : 2 * 148);
+  // compact launches: full tiles whose groups are 32, 64 or a multiple of 128 columns wide run one
+  // row per thread (a third slower per tile, on an eighth of the SMs)
+  const int gpt = !compact ? 0 : group % TILE == 0 ? 1 : group == 64 ? 2 : group == 32 ? 4 : 0;
+
   for (int64_t i1 = 0; i1 < C; i1 += TILE) {
     const int nb = (int)((C - i1) < TILE ? (C - i1) : TILE);
     {
@@ -353,10 +340,18 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       ProfScope prof(PROF_SWEEP_TILE, (double)R * nb * (4.0 + 1.0 + 4.0) + 2.0 * nb * nb, (double)R * nb * (nb - 1), st);
       sa.i1 = (int)i1; sa.nb = nb;
       if (tensor) sa.err_planes = err_set.base + (i1 % SUPER);
-      switch (out_dtype) {
-        case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
-        case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
-        default: MQ_TRY(launch_sweep_tile<MQ_F16>(chained, uniform, grid, st, sa));
+      if (gpt && nb == TILE) {
+        switch (out_dtype) {
+          case MQ_F32: MQ_TRY(launch_sweep_rows<MQ_F32>(chained, gpt, (int)R, st, sa)); break;
+          case MQ_BF16: MQ_TRY(launch_sweep_rows<MQ_BF16>(chained, gpt, (int)R, st, sa)); break;
+          default: MQ_TRY(launch_sweep_rows<MQ_F16>(chained, gpt, (int)R, st, sa));
+        }
+      } else {
+        switch (out_dtype) {
+          case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
+          case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
+          default: MQ_TRY(launch_sweep_tile<MQ_F16>(chained, uniform, grid, st, sa));
+        }
       }
     }
     MQ_LAUNCH_CHECK();
@@ -421,7 +416,8 @@ extern "C" int mq_gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const 
   MQ_REQUIRE(C % 8 == 0, MQ_ERR_UNSUPPORTED, "mq_gptq_sweep: C=%lld must be a multiple of 8", (long long)C);
   MQ_REQUIRE(ldw % 4 == 0 && ldu % 4 == 0 && aligned(W, 16) && aligned(Uhat, 16) && aligned(codes, 4), MQ_ERR_ALIGNMENT,
              "mq_gptq_sweep: W/Uhat need 16-byte alignment and leading dimensions that are multiples of 4");
-  MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_gptq_sweep: bad math %d", math);
+  MQ_REQUIRE((math & ~MQ_MATH_COMPACT) == MQ_MATH_FP32 || (math & ~MQ_MATH_COMPACT) == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT,
+             "mq_gptq_sweep: bad math %d", math);
   Workspace ws(workspace, workspace_bytes);
   if (W_original) {
     MQ_REQUIRE(ldwo >= C && ldwo % 4 == 0 && aligned(W_original, 16) && W_original != W, MQ_ERR_ALIGNMENT,

@@ -15,6 +15,7 @@ What differs from the reference, by design:
 from __future__ import annotations
 
 from enum import Enum
+import dataclasses
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -372,6 +373,26 @@ def _side_streams(device: torch.device, n: int):
     return pool[:n]
 
 
+class _compact_launches:
+    """While several layers are in flight on different streams, a handle asks the engine for launch
+    shapes that occupy few SMs (ops.Precision.compact); the results are the same bits."""
+
+    def __init__(self, handle: GPTQ, on: bool):
+        self.handle, self.on, self.saved = handle, on, None
+
+    def __enter__(self):
+        if self.on:
+            self.saved = self.handle.precision
+            base = ops.DEFAULT_PRECISION if self.saved is None else self.saved
+            self.handle.precision = dataclasses.replace(base, compact=True)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            self.handle.precision = self.saved
+        return False
+
+
 @torch.no_grad()
 def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 8) -> List[Tuple[Tensor, Tensor, Tensor]]:
     """Quantizes independent, non-distributed handles (the routed experts of a rank,
@@ -391,7 +412,7 @@ def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 8) -> List[
         s.wait_stream(current)
     out = []
     for i, h in enumerate(handles):
-        with torch.cuda.stream(pool[i % len(pool)]):
+        with torch.cuda.stream(pool[i % len(pool)]), _compact_launches(h, len(pool) > 1):
             out.append(h.quantize(bits))
     for s in pool:
         current.wait_stream(s)

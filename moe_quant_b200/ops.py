@@ -12,7 +12,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import MATH_FP32, MATH_TENSOR, MoeQuantError, check, dtype_code, lib, ptr, require_cuda, stream_ptr
+from ._lib import MATH_COMPACT, MATH_FP32, MATH_TENSOR, MoeQuantError, check, dtype_code, lib, ptr, require_cuda, stream_ptr
 
 
 @dataclass
@@ -23,12 +23,20 @@ class Precision:
     split_*: number of bf16 planes an fp32 operand is cut into on the tensor path
     (1, 2 or 3 planes -> 1, 3 or 6 products).  bf16/fp16 activations always enter the
     Hessian exactly with one product.
+    compact: several layers are in flight on different streams (quantize_many sets it): the sweep
+    uses launch shapes that occupy few SMs (MQ_MATH_COMPACT); the results do not change.
     """
 
     math: int = MATH_TENSOR
     split_hessian: int = 3
     split_hinv: int = 3
     split_sweep: int = 3
+    compact: bool = False
+
+    @property
+    def sweep_math(self) -> int:
+        """The `math` argument of the sweep and of the whole-layer entry point."""
+        return self.math | (MATH_COMPACT if self.compact else 0)
 
 
 DEFAULT_PRECISION = Precision()
@@ -210,7 +218,7 @@ def gptq_sweep(W: Tensor, Uhat: Tensor, scale: Tensor, zero: Optional[Tensor], g
     with torch.cuda.device(W.device):
         check(L.mq_gptq_sweep(ptr(W), R, C, W.stride(0), ptr(Uhat), Uhat.stride(0), ptr(scale), ptr(zero), group,
                               row_stride, group_stride, bits, dtype_code(dtype), ptr(codes), ptr(packed_out), ptr(deq),
-                              ptr(W_original), 0 if W_original is None else W_original.stride(0), p.math,
+                              ptr(W_original), 0 if W_original is None else W_original.stride(0), p.sweep_math,
                               p.split_sweep, ptr(ws), ws.numel(), stream_ptr(W.device)))
     return codes, deq
 
@@ -252,7 +260,7 @@ def quantize_layer(weights: Sequence[Tensor], H: Tensor, group: int, bits: int, 
     p_arr = arr(*[t.data_ptr() for t in packed]) if packed is not None else None
     with torch.cuda.device(dev):
         check(L.mq_quantize_layer(w_arr, dtype_code(dtype), n, R, C, ptr(H), H.stride(0), group, bits, rel_damp, c_arr,
-                                  p_arr, s_arr, d_arr, ptr(flags), p.math, p.split_hinv, p.split_sweep, ptr(ws), ws.numel(),
+                                  p_arr, s_arr, d_arr, ptr(flags), p.sweep_math, p.split_hinv, p.split_sweep, ptr(ws), ws.numel(),
                                   stream_ptr(dev)))
     if want_packed:
         return codes, scales, deqs, flags, packed

@@ -444,3 +444,39 @@ def test_mse_scales_match_oracle(cuda, R, C, g, dtype):
         return ((y - Wg).abs().log() * 2.4).exp().sum(-1)
 
     torch.testing.assert_close(loss(got), loss(want), rtol=1e-3, atol=0)
+
+
+# ------------------------------------------------------------------ compact launches
+@pytest.mark.parametrize("R,C,g,dtype,math", [(200, 512, 128, torch.bfloat16, MATH_TENSOR), (64, 384, 64, torch.float16, MATH_TENSOR),
+                                              (333, 640, 32, torch.float32, MATH_TENSOR), (130, 512, 512, torch.bfloat16, MATH_FP32),
+                                              (96, 392, 56, torch.float16, MATH_TENSOR)])
+def test_compact_sweep_is_bit_identical(cuda, R, C, g, dtype, math):
+    """MQ_MATH_COMPACT only changes the launch shape of the sweep's full tiles (one weight row per
+    thread instead of eight lanes per row): codes, dequantized values, packed words and scales
+    must be the same bits, through the whole-layer call and through the sweep alone with zero
+    points and the factor of the inverse (the reference's form of the recurrence).  The last case
+    (group 56, C = 3 tiles + 8) has no tile the row kernel takes and a narrow last tile."""
+    W = synthetic.layer_weight(R, C, 3, dtype).to(cuda)
+    X = synthetic.activations(2 * C, C, 4, dtype).to(cuda)
+    H = torch.zeros(C, C, device=cuda)
+    ops.hessian_accum(H, X, 0.0, 2.0 / X.shape[0])
+    outs = []
+    for compact in (False, True):
+        p = ops.Precision(math=math, compact=compact)
+        outs.append(ops.quantize_layer([W], H.clone(), g, 4, 1e-2, want_dequantized=True, precision=p, want_packed=True))
+    (c0, s0, d0, f0, p0), (c1, s1, d1, f1, p1) = outs
+    assert torch.equal(c0[0], c1[0]) and torch.equal(s0[0], s1[0]) and torch.equal(p0[0], p1[0])
+    assert torch.equal(d0[0].float(), d1[0].float()) and torch.equal(f0, f1)
+
+    # the sweep alone: factor of the inverse, per-group zero points
+    Hd = H.clone()
+    ops.hessian_prepare(Hd, W.float(), 1e-2)
+    U, _, _ = ops.hinv_upper(Hd, ops.Precision(math=math))
+    scale = ops.absmax_scales(W.float(), g, 4, dtype)
+    gen = torch.Generator().manual_seed(1)
+    zero = torch.randint(6, 11, scale.shape, generator=gen).float().to(cuda)
+    res = []
+    for compact in (False, True):
+        p = ops.Precision(math=math, compact=compact)
+        res.append(ops.gptq_sweep(W.float().clone(), U, scale, zero, g, C // g, 1, 4, dtype, True, p))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1].float(), res[1][1].float())

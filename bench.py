@@ -45,6 +45,8 @@ sys.path.insert(0, ROOT)
 R, C, TOKENS, GROUP, BITS = 2048, 7168, 4096, 128, 4
 WORKLOAD = "deepseek_v3_routed_expert_gate_proj_2048x7168_bf16_g128 (one rank's expert shard, Hessian resident)"
 METRIC = "GPTQ layers/sec (2048x7168, 4b g128)"
+# DRAM traffic of one 128 x 128 output tile of a 512-deep three-plane update (ncu, profiles/)
+DEEP_DRAM_BYTES_PER_TILE = 103.0e3
 CONFIG = {"workload": WORKLOAD, "rows": R, "cols": C, "bits": BITS, "group_size": GROUP, "rel_damp": 1e-2,
           "weight_dtype": "bf16", "calibration_tokens_mean": TOKENS}
 
@@ -400,27 +402,50 @@ def headline(cx):
         tot = sum(v["ms"] for v in kinds.values())
         shares = {k: round(v["ms"] / tot, 4) for k, v in kinds.items()}
         per_layer_us = {k: round(v["ms"] / n_prof * 1e3, 1) for k, v in kinds.items()}
+        # The tensor-core GEMMs (rank-128 updates inside a 512-column super-block: umma_gemm; the
+        # 512-deep updates behind it: umma_deep) are one family; when it has the largest share of the
+        # kernel time the roofline is that of its member with the most work, the deep update (nine
+        # tenths of a layer's flop, and the largest single share of a step once several layers run
+        # side by side and the latency-bound kernels overlap).  The other members follow in
+        # roofline["others"].
+        family = {k: kinds[k] for k in ("umma_gemm", "umma_deep") if k in kinds}
+        fam_ms = sum(v["ms"] for v in family.values())
+        if family and fam_ms >= max(v["ms"] for k, v in kinds.items() if k not in family):
+            top = max(family, key=lambda k: family[k]["work"])
         v = kinds[top]
-        if top in ("umma_gemm", "simt_gemm"):
+
+        def tensor_line(kind, v):
             secs = v["ms"] / 1e3
-            products = 6.0 if top == "umma_gemm" else 1.0     # bf16 products per fp32 product with three planes
+            products = 1.0 if kind == "simt_gemm" else 6.0     # bf16 products per fp32 product with three planes
             achieved = v["work"] * products / secs / 1e12
-            # DRAM bytes per 128 x 128 x 128 tile-update of C, from an ncu capture of two large launches
-            # of the rank-128 update (141.1 MB for 1485 tiles); a launch with a longer reduction touches
-            # its C tile once for all of it, so the figure is scaled by output tiles, not by flop
-            tile_updates = v["work2"] / v["launches"] / (2.0 * 128 * 128 * 128 * products)
-            roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
-                        "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
-                        "traffic": 95.0e3 * tile_updates if top == "umma_gemm" else None,
-                        "traffic_source": "scaled from an ncu capture (95 KB of DRAM traffic per 128x128 tile of a rank-128 "
-                                          "update), not measured in this run",
-                        "fp32_equivalent_tflops": v["work"] / secs / 1e12,
-                        "padded_tflops": v["work2"] / secs / 1e12,
-                        "note": "algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products "
-                                "per fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once; "
-                                "timed on one stream with full grids",
-                        "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / n_prof,
-                        "peak_source": peaks["source"] + " (sustained bf16)"}
+            return {"kernel": kind, "bound": "tensor", "achieved": achieved, "peak": peaks["tensor_sustained"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["tensor_sustained"],
+                    "fp32_equivalent_tflops": v["work"] / secs / 1e12, "padded_tflops": v["work2"] / secs / 1e12,
+                    "avg_launch_us": v["ms"] / v["launches"] * 1e3, "launches_per_layer": v["launches"] / n_prof,
+                    "share_of_kernel_time": round(v["ms"] / tot, 4)}
+
+        if top in ("umma_gemm", "umma_deep", "simt_gemm"):
+            roofline = tensor_line(top, v)
+            products = 1.0 if top == "simt_gemm" else 6.0
+            out_tiles = v["work2"] / v["launches"] / (2.0 * 128 * 128 * products)   # output tiles x k per launch
+            if top == "umma_deep":
+                # DRAM bytes per 128 x 128 output tile of a 512-deep update, from an ncu capture of the
+                # 6656 x 6656 x 512 upper-triangle update (profiles/): the C tile once in, once out, and
+                # the operand slabs that miss the L2
+                roofline["traffic"] = DEEP_DRAM_BYTES_PER_TILE * out_tiles / 512.0
+                roofline["traffic_source"] = ("scaled by output tiles from an ncu capture of one 512-deep update "
+                                              "(profiles/umma_stream_kernel_far_update.md), not measured in this run")
+            elif top == "umma_gemm":
+                roofline["traffic"] = 95.0e3 * out_tiles / 128.0
+                roofline["traffic_source"] = ("scaled from an ncu capture (95 KB of DRAM traffic per 128x128 tile of a "
+                                              "rank-128 update), not measured in this run")
+            else:
+                roofline["traffic"] = None
+            roofline["note"] = ("algorithmic work of the split-bf16 GEMM: 2MNK on the kept tiles x 6 bf16 tensor products per "
+                                "fp32 product (3 planes); fp32_equivalent_tflops counts each fp32 product once; timed on one "
+                                "stream with full grids; chosen as the member of the tensor-GEMM family with the most work")
+            roofline["peak_source"] = peaks["source"] + " (sustained bf16)"
+            roofline["others"] = [tensor_line(k, kv) for k, kv in family.items() if k != top]
         else:
             achieved = v["work"] / (v["ms"] / 1e3) / 1e9
             roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
@@ -860,8 +885,9 @@ def run_single_layer(args):
     X = _randn_acts(TOKENS, C, torch.bfloat16, 1, dev)
     H = torch.zeros(C, C, device=dev)
     ops.hessian_accum(H, X, 0.0, 2.0 / TOKENS)
+    precision = ops.Precision(compact=bool(args.compact))   # --compact: the launch shapes quantize_many asks for
     for _ in range(max(1, args.steps)):
-        ops.quantize_layer([W], H.clone(), GROUP, BITS, 1e-2)
+        ops.quantize_layer([W], H.clone(), GROUP, BITS, 1e-2, precision=precision)
     torch.cuda.synchronize()
     print(json.dumps({"single_layer": True, "launches": int(_lib.lib().mq_launch_count()),
                       "engine_fault": int(_lib.engine_fault())}))
@@ -879,6 +905,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single-layer", action="store_true",
                     help="run one Hessian accumulation and --steps layers untimed (profiler captures)")
+    ap.add_argument("--compact", action="store_true", help="with --single-layer: the compact launch shapes of quantize_many")
     args = ap.parse_args()
     if args.single_layer:
         run_single_layer(args)

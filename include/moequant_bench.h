@@ -23,9 +23,10 @@ long long mq_launch_count(void);
  * launches, summed milliseconds, and two work figures (GEMM kinds: algorithmic flop and
  * issued tensor flop; sweep: algorithmic bytes and flop; split/pack: bytes).
  * Not thread-safe; meant for one benchmarking thread.  */
-#define MQ_PROFILE_KINDS 8
+#define MQ_PROFILE_KINDS 9
 enum { MQ_PROF_UMMA_GEMM = 0, MQ_PROF_SIMT_GEMM = 1, MQ_PROF_SWEEP_TILE = 2, MQ_PROF_CHOL_DIAG = 3,
-       MQ_PROF_TRSM = 4, MQ_PROF_SPLIT = 5, MQ_PROF_PACK = 6, MQ_PROF_OTHER = 7 };
+       MQ_PROF_TRSM = 4, MQ_PROF_SPLIT = 5, MQ_PROF_PACK = 6, MQ_PROF_OTHER = 7,
+       MQ_PROF_UMMA_DEEP = 8 /* tensor GEMMs with more than 128 of k and several planes: the streaming kernel */ };
 int mq_profile_begin(void);
 int mq_profile_end(int64_t* launches, double* milliseconds, double* work, double* work2);
 

@@ -109,7 +109,7 @@ def engine_fault() -> int:
     return out.value
 
 
-PROFILE_KINDS = ["umma_gemm", "simt_gemm", "sweep_tile", "chol_diag", "trsm_rows", "split_planes", "pack_int4", "other"]
+PROFILE_KINDS = ["umma_gemm", "simt_gemm", "sweep_tile", "chol_diag", "trsm_rows", "split_planes", "pack_int4", "other", "umma_deep"]
 
 
 def profile_begin() -> None:

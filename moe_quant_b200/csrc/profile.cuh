@@ -8,7 +8,7 @@
 namespace mq {
 
 enum ProfKind { PROF_UMMA_GEMM = 0, PROF_SIMT_GEMM = 1, PROF_SWEEP_TILE = 2, PROF_CHOL_DIAG = 3, PROF_TRSM = 4,
-                PROF_SPLIT = 5, PROF_PACK = 6, PROF_OTHER = 7, PROF_KINDS = 8 };
+                PROF_SPLIT = 5, PROF_PACK = 6, PROF_OTHER = 7, PROF_UMMA_DEEP = 8, PROF_KINDS = 9 };
 
 extern bool g_profile_on;
 void prof_open(int kind, double work, double work2, cudaStream_t st);

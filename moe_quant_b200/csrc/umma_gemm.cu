@@ -1386,7 +1386,10 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
   dim3 grid((unsigned)ceil_div(d.N, TILE_N), (unsigned)ceil_div(d.M, TILE_M), (unsigned)d.batch);
   double flop_alg = 0.0, flop_issued = 0.0;
   if (g_profile_on) gemm_work(d, SLAB_K, &flop_alg, &flop_issued, p.nterms);
-  ProfScope prof(PROF_UMMA_GEMM, flop_alg, flop_issued, st);
+  const bool panel_route = d.K <= 2 * SLAB_K && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.K > 0 && !d.mirror_to_lower;
+  const bool deep_route = !panel_route && A.planes > 1 && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && !d.mirror_to_lower &&
+                          d.K > 2 * SLAB_K;
+  ProfScope prof(deep_route ? PROF_UMMA_DEEP : PROF_UMMA_GEMM, flop_alg, flop_issued, st);
   if (d.K <= 2 * SLAB_K && d.batch == 1 && !d.a_upper && !d.b_upper && !d.n_step && d.K > 0 && !d.mirror_to_lower) {
     // rank-<=128 update: keep A in shared memory and walk runs of n-tiles
     const int m_tiles = (int)ceil_div(d.M, TILE_M), n_tiles = (int)ceil_div(d.N, TILE_N);

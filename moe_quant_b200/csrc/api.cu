@@ -148,7 +148,7 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
     MQ_REQUIRE(!packed || (packed[i] && bits == 4 && aligned(packed[i], 4)), MQ_ERR_UNSUPPORTED,
                "mq_quantize_layer: packed words need bits == 4 and a 4-byte aligned buffer per layer");
   }
-  const int sweep_math = math;   // the sweep honours MQ_MATH_COMPACT
+  const int sweep_math = math;   // the factorisation and the sweep honour MQ_MATH_COMPACT
   math &= ~MQ_MATH_COMPACT;
   MQ_REQUIRE(math == MQ_MATH_FP32 || math == MQ_MATH_TENSOR, MQ_ERR_ARGUMENT, "mq_quantize_layer: bad math %d", sweep_math);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -186,7 +186,7 @@ extern "C" int mq_quantize_layer(const void* const* Wsrc, int w_dtype, int n_tie
   MQ_LAUNCH_CHECK();
   {
     Workspace sub(ws.base + ws.used, ws.size - ws.used);
-    MQ_TRY(chol_unit_factor(U, C, C, diag, math, split_hinv, flags, sub, st, true, unscaled));
+    MQ_TRY(chol_unit_factor(U, C, C, diag, sweep_math, split_hinv, flags, sub, st, true, unscaled));
   }
   // sweep                                                       src/gptq_loop.py:141-148
   for (int i = 0; i < n_tied; ++i) {

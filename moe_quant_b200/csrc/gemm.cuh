@@ -33,6 +33,9 @@ struct GemmDesc {
   // columns of k are added to C one after the other in round-to-nearest fp32, as separate
   // updates of depth k_round would, instead of meeting inside the tensor core's accumulator.
   int k_round = 0;
+  // Tensor path, rank-<=128 updates: the caller runs several layers at once (MQ_MATH_COMPACT), so
+  // a CTA walks a whole row of output tiles: half to a third of the CTAs, each a little longer.
+  int compact = 0;
 };
 
 // fp32 CUDA-core implementation; in_dtype is the element type of A and B.

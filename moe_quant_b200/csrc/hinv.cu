@@ -476,6 +476,8 @@ size_t hinv_workspace_bytes(int64_t C, int math, int split) {
 int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, int split, mq_layer_flags* flags,
                      Workspace& ws, cudaStream_t st, bool upper_only, bool unscaled) {
   MQ_TRY(configure_once());
+  const int compact = (math & MQ_MATH_COMPACT) ? 1 : 0;   // only the rank-128 strips look at it
+  math &= ~MQ_MATH_COMPACT;
   Engine eng(math, split, ws, st);
   const int P = (int)ceil_div(C, NB);
   // Tensor path: the panel solve writes its result as bf16 planes too, and the rank-128 update
@@ -536,6 +538,7 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
         g.C = H + k0; g.ldc = ldh;
         g.M = (int)k1; g.N = (int)(k1 - k0); g.K = nb;
         g.alpha = -1.0f; g.beta = 1.0f;
+        g.compact = compact;
         PlaneSet a = pset, b = pset;
         a.k0 = kwin;
         b.k0 = kwin; b.row0 = k0;

@@ -375,6 +375,7 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
       g.C = W + i2; g.ldc = ldw;
       g.M = (int)R; g.N = (int)(s1 - i2); g.K = nb;
       g.alpha = 1.0f; g.beta = 1.0f;
+      g.compact = compact ? 1 : 0;
       PlaneSet a = err_set, b = u_set;
       a.k0 = (int)(i1 - s0);
       b.row0 = i2; b.k0 = (int)i1;

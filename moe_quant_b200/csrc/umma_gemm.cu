@@ -1411,6 +1411,7 @@ int launch_umma(const GemmDesc& d, const PlaneSet& A, const PlaneSet& B, cudaStr
         if (cost < best) { best = cost; run = cand; }
       }
     }
+    if (d.compact) run = n_tiles < PANEL_MAX_RUN ? n_tiles : PANEL_MAX_RUN;
     dim3 pgrid((unsigned)ceil_div(n_tiles, run), (unsigned)m_tiles, 1);
     // C goes through the TMA unit when the map can be built (16-byte aligned rows, and a beta
     // that a plain store (0) or an add at the L2 (1) expresses) and every SM has at least two

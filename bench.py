@@ -19,8 +19,10 @@ Printed JSON (one line, rank 0):
   e2e        layers/s through the public handles with HOST buffers: per expert the calibration
              activations and the gate_proj / up_proj weights are copied from pinned memory, the
              Hessian is accumulated, both layers are quantized, codes and scales copied back
-  roofline   the kernel family that takes the largest share of a step, timed with CUDA events on
-             its launching stream by the library's measurement hooks in a separate pass
+  roofline   the tensor-core GEMMs take the largest share of a step; of that family the 512-deep
+             update (nine tenths of a layer's flop), timed with CUDA events on its launching stream
+             by the library's measurement hooks in a separate pass; the family's other member
+             follows in roofline.others and every family's share in kernel_time_shares
   parity     code agreement of one sampled step with the CPU oracle on a slice of rows (untimed)
   cpu_baseline  the CPU oracle (a port of the reference's torch path) on this box's cores
   extra      the other named workloads (`--workload all`, the default): expert down_proj with the

@@ -14,7 +14,10 @@
 //   1. chol_diag_rev_kernel  : the 128x128 diagonal block, one CTA, register tiled;
 //   2. trsm_rows_kernel      : the panel above it, one warp per row, substitution
 //                              against the diagonal block staged in shared memory;
-//   3. a GEMM (GemmDesc)     : trailing update of the upper triangle.
+//   3. GEMMs (GemmDesc)      : trailing update of the upper triangle; on the tensor path in two
+//                              levels (the rest of the panel's 512-column super-panel at once,
+//                              everything in front of the super-panel once per super-panel with
+//                              all 512 columns in the contraction).
 // The inverse is built by inverting the 128x128 diagonal blocks (same substitution
 // kernel on identity rows) and then merging neighbouring blocks pairwise,
 //   inv([A B; 0 D]) = [A^-1, -A^-1 B D^-1; 0, D^-1],

@@ -12,11 +12,17 @@
 // tile is eight such chains back to back; after a chain its sixteen errors are broadcast with
 // shuffles and the other lanes of the row apply them to their columns.  Rows are independent:
 // no block-wide synchronisation after the tile of Uhat is staged in shared memory.
+// (sweep_rows.cuh holds the same tile with one row per thread, for callers that run several
+// layers at once.)
 //
-// The errors of the tile (R x 128) go to a scratch matrix and the lazy update
+// The errors of the tile (R x 128) go to a scratch matrix, as bf16 planes on the tensor path,
+// and the lazy update
 //   W[:, later] += E Uhat[tile, later]             (src/gptq_loop.py:148)
-// is a GEMM through the Engine.  Codes are written straight into the (R, C) uint8
-// result, so the transposes of src/gptq.py:191-199 never happen.
+// is a GEMM: on the tensor path in two levels (the rest of the tile's 512-column super-block at
+// once, everything behind the super-block once per super-block with all 512 errors of a row
+// in the contraction), on the fp32 path one update of everything behind the tile.  Codes are
+// written straight into the (R, C) uint8 result, so the transposes of src/gptq.py:191-199
+// never happen.
 #include "engine.cuh"
 #include "profile.cuh"
 #include "sweep.cuh"

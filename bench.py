@@ -315,6 +315,7 @@ def headline(cx):
     import torch.nn as nn
 
     from moe_quant_b200 import GPTQ, _lib, ops, quantize_many, quantize_tied, synthetic
+    from moe_quant_b200.gptq import compact_launches
 
     dev, world, rank = cx.dev, cx.world, cx.rank
     steps, n_streams, barrier = cx.steps, cx.n_streams, cx.barrier
@@ -471,16 +472,8 @@ def headline(cx):
         return out
 
     def run_pairs(pairs):
-        cur = torch.cuda.current_stream(dev)
-        for st in pair_pool:
-            st.wait_stream(cur)
-        res = []
-        for i, (g_h, u_h) in enumerate(pairs):
-            with torch.cuda.stream(pair_pool[i % len(pair_pool)]):
-                res.append(quantize_tied([g_h, u_h], BITS))
-        for st in pair_pool:
-            cur.wait_stream(st)
-        return res
+        # quantize_many groups each up_proj with the gate_proj it is tied to: one factorisation per pair
+        return quantize_many([h for pair in pairs for h in pair], BITS, streams=len(pair_pool))
 
     pre_pairs = run_pairs(make_pairs(n_pairs))
     barrier()
@@ -535,7 +528,9 @@ def headline(cx):
         gate = GPTQ(_linear(Wg), GROUP, True, 1e-2, 128)
         up = GPTQ(_linear(Wu), GROUP, True, 1e-2, 128, tied_gptq_handle=gate)
         gate.update(Xd)
-        for j, (q, s, _z) in enumerate(quantize_tied([gate, up], BITS)):
+        with compact_launches(gate, n_streams > 1):   # several pairs are in flight on the other streams
+            pair_res = quantize_tied([gate, up], BITS)
+        for j, (q, s, _z) in enumerate(pair_res):
             q_host[k][j].copy_(q, non_blocking=True)
             s_host[k][j].copy_(s, non_blocking=True)
         gate.reset()
@@ -782,16 +777,9 @@ def wl_moe_layer(cx):
             gates[e].update(Xs[e])
             downs[e].update(Xd[e])
         e1.record()
-        cur = torch.cuda.current_stream(dev)
-        for st in pool:
-            st.wait_stream(cur)
-        res = []
-        for e in range(n_exp):
-            with torch.cuda.stream(pool[e % len(pool)]):
-                res.append(quantize_tied([gates[e], ups[e]], BITS))
-        for st in pool:
-            cur.wait_stream(st)
-        res.append(quantize_many(downs, BITS, streams=cx.n_streams))
+        # every expert's layers in one call: gate/up pairs share a factorisation, pairs and down_proj
+        # layers of different experts run side by side (what block_driver.quantize_block does)
+        res = quantize_many([h for e in range(n_exp) for h in (gates[e], ups[e], downs[e])], BITS, streams=cx.n_streams)
         e2.record()
         torch.cuda.synchronize()
         issues = sum(h.has_hessian_issues() for h in gates + ups + downs)

@@ -56,7 +56,7 @@ typedef enum { MQ_MATH_FP32 = 0, MQ_MATH_TENSOR = 1 } mq_math;
  * their *_workspace_bytes): the caller processes several layers at once on different streams
  * (gptq.quantize_many).  The library then prefers launch shapes that occupy few SMs over the
  * lowest latency of a single layer: the sweep's tiles run one weight row per thread on R/64
- * SMs instead of eight lanes per row on R/16, and a CTA of a rank-128 strip update walks a whole
+ * SMs instead of sixteen lanes per row on R/8 CTAs, and a CTA of a rank-128 strip update walks a whole
  * row of output tiles.  Results are bit-identical with and without it. */
 #define MQ_MATH_COMPACT 0x100
 

@@ -6,7 +6,7 @@ and recompute the block's outputs as the next block's inputs.
 
 Differences from the reference loop, all on the throughput side: routed experts are quantized
 several at a time on CUDA streams (`quantize_many`), and with `tie_gptq_handles` a gate/up pair
-shares one factorisation (`quantize_tied`).  The saved tensors are what the reference saves.
+shares one factorisation (`quantize_many` groups tied handles).  The saved tensors are what the reference saves.
 """
 from __future__ import annotations
 
@@ -19,7 +19,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import dist_utils, model_utils, quant_utils
-from .gptq import GPTQ, quantize_many, quantize_shared, quantize_tied
+from .gptq import GPTQ, quantize_many, quantize_shared
 
 ROUTED_EXPERTS_REGEX = r".*mlp\.experts\.\d+\.(down|gate|up)_proj$"   # quant.py:24
 
@@ -121,18 +121,9 @@ def quantize_block(
         handles[name].reset()
 
     # routed experts: independent of each other and of other ranks (quant.py:351-387)
+    # (with tie_gptq_handles an up_proj handle is tied to its gate_proj: quantize_many gives each
+    # such pair one factorisation)
     pending = list(experts)
-    if tie_gptq_handles:
-        for name in list(pending):
-            h = handles[name]
-            if h.tied_gptq_handle is not None:
-                gate = name.rsplit(".", 1)[0] + ".gate_proj"
-                if gate in pending:
-                    res = quantize_tied([handles[gate], h], bits)
-                    finish(gate, res[0], main_only=False)
-                    finish(name, res[1], main_only=False)
-                    pending.remove(gate)
-                    pending.remove(name)
     results = quantize_many([handles[n] for n in pending], bits, streams=streams)
     for name, res in zip(pending, results):
         finish(name, res, main_only=False)

@@ -2,14 +2,14 @@
 // reference's captured loop (src/gptq_loop.py:141-148) with, per 128-column tile,
 // ONE sweep kernel plus ONE GEMM.
 //
-// Sweep kernel: eight lanes share one weight row, lane l keeps columns 16l..16l+15 of the
-// current tile in registers (four rows per warp).  Column j is quantized as
+// Sweep kernel: sixteen lanes share one weight row, lane l keeps columns 8l..8l+7 of the
+// current tile in registers (two rows per warp).  Column j is quantized as
 //   q = clamp(floor(x/s + z + 0.5), 0, maxq)   y = round_to_dtype((q - z) s)   e = y - x
 // (src/gptq_loop.py:28-40, src/quant_utils.py:30-49) and its error is applied to the columns
 // behind it, w_k += Uhat[j,k] e (src/gptq_loop.py:83-88), with one fma per (j, k) in
-// increasing j: the reference's order.  The sixteen columns of a lane are a chain that needs
+// increasing j: the reference's order.  The eight columns of a lane are a chain that needs
 // no communication (the lane applies each error to its own later columns at once), so the
-// tile is eight such chains back to back; after a chain its sixteen errors are broadcast with
+// tile is sixteen such chains back to back; after a chain its eight errors are broadcast with
 // shuffles and the other lanes of the row apply them to their columns.  Rows are independent:
 // no block-wide synchronisation after the tile of Uhat is staged in shared memory.
 // (sweep_rows.cuh holds the same tile with one row per thread, for callers that run several
@@ -33,14 +33,24 @@ namespace mq {
 namespace {
 
 constexpr int TILE = SWEEP_TILE;
-constexpr int ROW_LANES = 8;                             // lanes that share one weight row
-constexpr int LANE_COLS = TILE / ROW_LANES;              // 16 consecutive columns per lane
-// THREADS per CTA is a template parameter (128, 256 or 512): THREADS / 8 rows per CTA
-// The tile of the factor in shared memory: row j holds eight chunks of 16 columns, 20 floats
-// apart, so that the eight lanes of a row read their chunks from disjoint groups of banks.
-constexpr int U_LANE_LD = LANE_COLS + 4;
-constexpr int U_ROW_LD = ROW_LANES * U_LANE_LD;          // 160 floats
-constexpr size_t kSweepSmem = (size_t)TILE * U_ROW_LD * sizeof(float);
+constexpr int TILE_THREADS = 128;                        // threads per CTA of the lane-per-chunk kernel
+// LANES lanes share one weight row and keep TILE / LANES consecutive columns each.  Sixteen lanes
+// (8 columns, 8 rows per CTA) give the shorter serial stream per warp: 4.83 against 5.03 ms per
+// 2048 x 7168 layer on one stream (with 256 threads per CTA 4.95 ms); a layer with more rows than
+// the grid holds at that shape walks its row groups in turns, and eight lanes (16 columns, 16 rows
+// per CTA) are faster again (7168 x 2048: 623 against 586 layers/s).  4 columns per lane would
+// need shuffles to form the 8-column vectors in which codes, packed words and error planes leave.
+// The tile of the factor in shared memory: row j holds LANES chunks, 4 floats of padding after
+// each, so that the lanes of a quarter-warp read their 16-byte pieces from disjoint banks.
+template <int LANES>
+struct LaneShape {
+  static constexpr int ROW_LANES = LANES;
+  static constexpr int LANE_COLS = TILE / LANES;
+  static constexpr int U_LANE_LD = LANE_COLS + 4;
+  static constexpr int U_ROW_LD = LANES * U_LANE_LD;       // 160 floats for 8 lanes, 192 for 16
+  static constexpr size_t smem = (size_t)TILE * U_ROW_LD * sizeof(float);
+};
+constexpr int MAX_SWEEP_CTAS = 2 * 148;
 // Four tiles form a super-block of 512 columns.  Behind each tile only the rest of its own
 // super-block takes the rank-128 update at once; the columns behind the super-block are updated
 // once per super-block with all 512 errors of a row in one contraction, so a tile of W is read
@@ -52,41 +62,47 @@ constexpr int SUPER = 4 * TILE;
 // all in flight at once; a copy with source size 0 writes zeros: everything below the diagonal
 // and past nb); trim: wait for them and zero the entries on and below the diagonal inside each
 // row's diagonal quad.  Every thread of the CTA must call both.
+template <int LANES>
 __device__ __forceinline__ void stage_factor_tile(float* ublk, const float* __restrict__ src, int64_t ldu, int nb) {
+  constexpr int LANE_COLS = LaneShape<LANES>::LANE_COLS, U_LANE_LD = LaneShape<LANES>::U_LANE_LD, U_ROW_LD = LaneShape<LANES>::U_ROW_LD;
   for (int idx = threadIdx.x; idx < TILE * TILE / 4; idx += blockDim.x) {
     const int j = idx >> 5, k4 = (idx & 31) * 4;
     const bool keep = j < nb && k4 < nb && k4 + 3 > j;
-    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&ublk[j * U_ROW_LD + (k4 >> 4) * U_LANE_LD + (k4 & 15)]);
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&ublk[j * U_ROW_LD + (k4 / LANE_COLS) * U_LANE_LD + (k4 % LANE_COLS)]);
     const float* g = keep ? src + (int64_t)j * ldu + k4 : src;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g), "r"(keep ? 16 : 0) : "memory");
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+template <int LANES>
 __device__ __forceinline__ void trim_factor_tile(float* ublk, int nb) {
+  constexpr int LANE_COLS = LaneShape<LANES>::LANE_COLS, U_LANE_LD = LaneShape<LANES>::U_LANE_LD, U_ROW_LD = LaneShape<LANES>::U_ROW_LD;
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   for (int j = threadIdx.x; j < nb; j += blockDim.x) {
     const int k4 = j & ~3;
-    float* q = &ublk[j * U_ROW_LD + (k4 >> 4) * U_LANE_LD + (k4 & 15)];
+    float* q = &ublk[j * U_ROW_LD + (k4 / LANE_COLS) * U_LANE_LD + (k4 % LANE_COLS)];
     for (int k = 0; k <= (j & 3); ++k) q[k] = 0.0f;
   }
   __syncthreads();
 }
 
-// UNIFORM: the sixteen columns of a lane lie in one quantization group (group % 16 == 0).
-template <int DT, bool UNIFORM, int THREADS>
-__global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) {
-  constexpr int ROWS_PER_CTA = THREADS / ROW_LANES;
+// UNIFORM: the columns of a lane lie in one quantization group (group % LANE_COLS == 0).
+template <int DT, bool UNIFORM, int LANES>
+__global__ void __launch_bounds__(TILE_THREADS) sweep_tile_kernel(const SweepArgs a) {
+  constexpr int ROW_LANES = LANES, LANE_COLS = LaneShape<LANES>::LANE_COLS;
+  constexpr int U_LANE_LD = LaneShape<LANES>::U_LANE_LD, U_ROW_LD = LaneShape<LANES>::U_ROW_LD;
+  constexpr int ROWS_PER_CTA = TILE_THREADS / ROW_LANES;
   using T = typename StorageOf<DT>::type;
   extern __shared__ __align__(16) float ublk[];  // [TILE][U_ROW_LD], strict upper triangle of the tile, 0 elsewhere
   const int nb = a.nb, i1 = a.i1;
   // The factor is constant during the sweep: its tile is staged before this grid waits for the
   // rank-128 update that precedes it in the stream (only W depends on that update).
-  stage_factor_tile(ublk, a.U + (int64_t)i1 * a.ldu + i1, a.ldu, nb);
+  stage_factor_tile<LANES>(ublk, a.U + (int64_t)i1 * a.ldu + i1, a.ldu, nb);
   chain_wait();
   chain_release();
-  trim_factor_tile(ublk, nb);
+  trim_factor_tile<LANES>(ublk, nb);
 
   const int sub = threadIdx.x & (ROW_LANES - 1);   // this lane's chunk of the row
   const int c_local = sub * LANE_COLS;
@@ -102,7 +118,7 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
 
   // the CTA walks row groups together (the shuffles below are warp-wide); rows past R carry zeros
   for (int rg = blockIdx.x; rg < row_groups; rg += gridDim.x) {
-    const int r = rg * ROWS_PER_CTA + (threadIdx.x >> 3);
+    const int r = rg * ROWS_PER_CTA + (threadIdx.x / ROW_LANES);
     const bool valid = r < a.R;
     float w[LANE_COLS], wo[LANE_COLS];
 #pragma unroll
@@ -131,7 +147,7 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
       }
       rs[t] = 1.0f / sc[t];
     }
-    // what this lane produces when its turn comes: the errors of its sixteen columns and their
+    // what this lane produces when its turn comes: the errors of its columns and their
     // codes, two to a float (q0 + 256 q1 is exact for codes below 256)
     float e[LANE_COLS], qacc[LANE_COLS / 2];
 #pragma unroll
@@ -142,8 +158,8 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
 #pragma unroll 1
     for (int lo = 0; lo < n_owner; ++lo) {
       if (sub == lo) {
-        // Chain of this lane's sixteen columns against its diagonal 16 x 16 block of the factor
-        // (the four lanes of the warp that own chunk `lo` of their rows run it; the others wait).
+        // Chain of this lane's columns against its diagonal LANE_COLS x LANE_COLS block of the factor
+        // (the lanes of the warp that own chunk `lo` of their rows run it; the others wait).
         // A step applies the error to the whole quad rows behind it: entries on and below the
         // diagonal are zero in the staged tile and the columns they touch are finished.
         const float* ud = &ublk[(lo * LANE_COLS) * U_ROW_LD + lo * U_LANE_LD];
@@ -169,7 +185,7 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
         }
       }
       __syncwarp();
-      // The sixteen errors of lane lo reach the other lanes of the row, which apply them to their
+      // The errors of lane lo reach the other lanes of the row, which apply them to their
       // own columns in the same order, with the same FMAs, as a one-column-at-a-time recurrence.
       // (For the lanes in front of lo the staged factor holds zeros; lane lo's own values are
       // not needed any more.)
@@ -189,7 +205,7 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
       }
     }
 
-    // ---- every lane writes what its sixteen columns produced
+    // ---- every lane writes what its columns produced
     if (valid) {
 #pragma unroll
       for (int qd = 0; qd < LANE_COLS / 4; ++qd) {
@@ -230,15 +246,13 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
           lp[t >> 1] = (uint32_t)l0 | ((uint32_t)l1 << 16);
         }
         uint16_t* dst = a.err_planes + (int64_t)r * a.err_ld + c_local;
-        reinterpret_cast<uint4*>(dst)[0] = make_uint4(hp[0], hp[1], hp[2], hp[3]);
-        reinterpret_cast<uint4*>(dst)[1] = make_uint4(hp[4], hp[5], hp[6], hp[7]);
-        if (a.n_planes > 1) {
-          reinterpret_cast<uint4*>(dst + a.plane_stride)[0] = make_uint4(mp[0], mp[1], mp[2], mp[3]);
-          reinterpret_cast<uint4*>(dst + a.plane_stride)[1] = make_uint4(mp[4], mp[5], mp[6], mp[7]);
-        }
-        if (a.n_planes > 2) {
-          reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[0] = make_uint4(lp[0], lp[1], lp[2], lp[3]);
-          reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[1] = make_uint4(lp[4], lp[5], lp[6], lp[7]);
+#pragma unroll
+        for (int v = 0; v < LANE_COLS / 8; ++v) {
+          reinterpret_cast<uint4*>(dst)[v] = make_uint4(hp[4 * v], hp[4 * v + 1], hp[4 * v + 2], hp[4 * v + 3]);
+          if (a.n_planes > 1)
+            reinterpret_cast<uint4*>(dst + a.plane_stride)[v] = make_uint4(mp[4 * v], mp[4 * v + 1], mp[4 * v + 2], mp[4 * v + 3]);
+          if (a.n_planes > 2)
+            reinterpret_cast<uint4*>(dst + 2 * a.plane_stride)[v] = make_uint4(lp[4 * v], lp[4 * v + 1], lp[4 * v + 2], lp[4 * v + 3]);
         }
       } else {
         float4* dst = reinterpret_cast<float4*>(a.err + (int64_t)r * a.err_ld + c_local);
@@ -250,16 +264,23 @@ __global__ void __launch_bounds__(THREADS) sweep_tile_kernel(const SweepArgs a) 
 }
 
 template <int DT>
-int launch_sweep_tile(bool chained, bool uniform, int grid, cudaStream_t st, const SweepArgs& args) {
-  if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true, 128>, dim3(grid), dim3(128), kSweepSmem, st, args));
-  else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false, 128>, dim3(grid), dim3(128), kSweepSmem, st, args));
+int launch_sweep_tile(bool chained, bool uniform, int lanes, int grid, cudaStream_t st, const SweepArgs& args) {
+  if (lanes == 16) {
+    if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true, 16>, dim3(grid), dim3(TILE_THREADS), LaneShape<16>::smem, st, args));
+    else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false, 16>, dim3(grid), dim3(TILE_THREADS), LaneShape<16>::smem, st, args));
+  } else {
+    if (uniform) MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, true, 8>, dim3(grid), dim3(TILE_THREADS), LaneShape<8>::smem, st, args));
+    else MQ_CUDA(launch_chained(chained, sweep_tile_kernel<DT, false, 8>, dim3(grid), dim3(TILE_THREADS), LaneShape<8>::smem, st, args));
+  }
   return MQ_OK;
 }
 
 template <int DT>
 int configure_dtype() {
-  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
-  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSweepSmem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LaneShape<8>::smem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LaneShape<8>::smem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LaneShape<16>::smem));
+  MQ_CUDA(cudaFuncSetAttribute(sweep_tile_kernel<DT, false, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LaneShape<16>::smem));
   return MQ_OK;
 }
 
@@ -327,11 +348,13 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
   sa.n_planes = split;
   sa.err_ld = tensor ? SUPER : TILE;
   sa.bits = bits;
-  const bool uniform = group % LANE_COLS == 0;
+  // sixteen lanes per row while the grid holds every row group at once, eight beyond that
+  const int lanes = ceil_div(R, TILE_THREADS / 16) <= MAX_SWEEP_CTAS ? 16 : 8;
+  const bool uniform = group % (TILE / lanes) == 0;
   // every CTA stages the tile of the factor once and then walks row groups: no more CTAs than
   // two per SM, so that a tall layer does not stage the same tile thousands of times
-  const int64_t row_groups = ceil_div(R, 128 / ROW_LANES);
-  const int grid = (int)(row_groups < 2 * 148 ? row_groups : 2 * 148);
+  const int64_t row_groups = ceil_div(R, TILE_THREADS / lanes);
+  const int grid = (int)(row_groups < MAX_SWEEP_CTAS ? row_groups : MAX_SWEEP_CTAS);
   // compact launches: full tiles whose groups are 32, 64 or a multiple of 128 columns wide run one
   // row per thread (a third slower per tile, on an eighth of the SMs)
   const int gpt = !compact ? 0 : group % TILE == 0 ? 1 : group == 64 ? 2 : group == 32 ? 4 : 0;
@@ -354,9 +377,9 @@ int gptq_sweep(float* W, int64_t R, int64_t C, int64_t ldw, const float* Uhat, i
         }
       } else {
         switch (out_dtype) {
-          case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, grid, st, sa)); break;
-          case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, grid, st, sa)); break;
-          default: MQ_TRY(launch_sweep_tile<MQ_F16>(chained, uniform, grid, st, sa));
+          case MQ_F32: MQ_TRY(launch_sweep_tile<MQ_F32>(chained, uniform, lanes, grid, st, sa)); break;
+          case MQ_BF16: MQ_TRY(launch_sweep_tile<MQ_BF16>(chained, uniform, lanes, grid, st, sa)); break;
+          default: MQ_TRY(launch_sweep_tile<MQ_F16>(chained, uniform, lanes, grid, st, sa));
         }
       }
     }

@@ -373,11 +373,13 @@ def _side_streams(device: torch.device, n: int):
     return pool[:n]
 
 
-class _compact_launches:
+class compact_launches:
     """While several layers are in flight on different streams, a handle asks the engine for launch
-    shapes that occupy few SMs (ops.Precision.compact); the results are the same bits."""
+    shapes that occupy few SMs (ops.Precision.compact); the results are the same bits.
+    `quantize_many` wraps its calls in this; a caller that spreads `quantize` / `quantize_tied`
+    calls over streams of its own uses it the same way (for tied handles, on the owner)."""
 
-    def __init__(self, handle: GPTQ, on: bool):
+    def __init__(self, handle: GPTQ, on: bool = True):
         self.handle, self.on, self.saved = handle, on, None
 
     def __enter__(self):
@@ -393,27 +395,46 @@ class _compact_launches:
         return False
 
 
+def _tied_groups(handles: Sequence[GPTQ]) -> List[List[int]]:
+    """Indices of `handles` grouped by shared Hessian: a handle that owns its Hessian leads the
+    handles of the list that are tied to it; a tied handle whose owner is not in the list stands
+    alone."""
+    groups: List[List[int]] = []
+    for i, h in enumerate(handles):
+        if h.tied_gptq_handle is None:
+            groups.append([i] + [j for j, t in enumerate(handles) if t.tied_gptq_handle is h])
+        elif not any(h.tied_gptq_handle is t for t in handles):
+            groups.append([i])
+    return groups
+
+
 @torch.no_grad()
 def quantize_many(handles: Sequence[GPTQ], bits: int, streams: int = 8) -> List[Tuple[Tensor, Tensor, Tensor]]:
     """Quantizes independent, non-distributed handles (the routed experts of a rank,
     quant.py:351-387) round-robin on `streams` CUDA streams.  One layer's GPTQ is a long chain of
     dependent kernels, many of them too small to fill 148 SMs; chains of different layers have no
-    dependency on each other, so running a few side by side fills the machine.  Results are the
-    same tensors handle.quantize(bits) returns, in the order of `handles`, ready for use on the
-    stream that was current at the call."""
+    dependency on each other, so running a few side by side fills the machine.  Handles of the
+    list that are tied to another handle of the list (gate_proj / up_proj of an expert with
+    --tie_gptq_handles) are quantized with it, one factorisation per group (`quantize_tied`).
+    Results are the same tensors handle.quantize(bits) returns, in the order of `handles`, ready
+    for use on the stream that was current at the call."""
     if not handles:
         return []
     if any(h.is_distributed for h in handles):
         raise MoeQuantError("quantize_many is for non-distributed handles; distributed ones broadcast their results")
     device = handles[0].W_device
     current = torch.cuda.current_stream(device)
-    pool = _side_streams(device, max(1, min(streams, len(handles))))
+    groups = _tied_groups(handles)
+    pool = _side_streams(device, max(1, min(streams, len(groups))))
     for s in pool:
         s.wait_stream(current)
-    out = []
-    for i, h in enumerate(handles):
-        with torch.cuda.stream(pool[i % len(pool)]), _compact_launches(h, len(pool) > 1):
-            out.append(h.quantize(bits))
+    out: List[Optional[Tuple[Tensor, Tensor, Tensor]]] = [None] * len(handles)
+    for k, grp in enumerate(groups):
+        hs = [handles[i] for i in grp]
+        with torch.cuda.stream(pool[k % len(pool)]), compact_launches(hs[0], len(pool) > 1):
+            res = quantize_tied(hs, bits) if len(hs) > 1 else [hs[0].quantize(bits)]
+        for i, r in zip(grp, res):
+            out[i] = r
     for s in pool:
         current.wait_stream(s)
     for res in out:

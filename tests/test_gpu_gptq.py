@@ -227,6 +227,46 @@ def test_quantize_many_streams_match_sequential(cuda, precision):
         assert torch.equal(q1, q2) and torch.equal(s1, s2) and torch.equal(z1, z2)
 
 
+def test_quantize_many_groups_tied_handles(cuda, precision):
+    """Handles of the list that are tied to another handle of the list (gate_proj / up_proj with
+    --tie_gptq_handles) are quantized with it, one factorisation per group, side by side with
+    the untied ones; every result equals what quantize_tied / quantize give for that group alone."""
+    from moe_quant_b200 import quantize_many
+    R, C, N = 72, 640, 700
+    Ws = [synthetic.layer_weight(R, C, 60 + i, torch.bfloat16) for i in range(7)]
+    Xs = [synthetic.activations(N + 11 * i, C, 80 + i, torch.bfloat16) for i in range(3)]
+
+    def handles():
+        hs = []
+        for e in range(3):                                    # gate, up (tied to gate), and an untied layer per expert
+            gate = GPTQ(_layer(Ws[2 * e], cuda), 128, True, 1e-2, 128, precision=precision)
+            gate.update(Xs[e].to(cuda))
+            up = GPTQ(_layer(Ws[2 * e + 1], cuda), 128, True, 1e-2, 128, precision=precision, tied_gptq_handle=gate)
+            other = GPTQ(_layer(Ws[6], cuda), 128, True, 1e-2, 128, precision=precision)
+            other.update(Xs[(e + 1) % 3].to(cuda))
+            hs += [up, other, gate] if e == 1 else [gate, up, other]   # order inside the list does not matter
+        return hs
+
+    # one group at a time on the current stream: quantize_tied for a pair, quantize for a single handle
+    from moe_quant_b200 import quantize_tied
+    hs_seq = handles()
+    want = [None] * len(hs_seq)
+    for i, h in enumerate(hs_seq):
+        if h.tied_gptq_handle is not None:
+            continue
+        tied = [j for j, t in enumerate(hs_seq) if t.tied_gptq_handle is h]
+        if tied:
+            for j, r in zip([i] + tied, quantize_tied([h] + [hs_seq[j] for j in tied], 4)):
+                want[j] = r
+        else:
+            want[i] = h.quantize(4)
+    got = quantize_many(handles(), 4, streams=4)
+    torch.cuda.synchronize()
+    assert len(got) == len(want)
+    for (q1, s1, z1), (q2, s2, z2) in zip(want, got):
+        assert torch.equal(q1, q2) and torch.equal(s1, s2) and torch.equal(z1, z2)
+
+
 def test_conv_layer_goes_through_unfold(cuda, precision):
     """Convolutions are handled like the reference does: inputs unfolded to patches
     (src/gptq.py:87-96), weight flattened to (out, in*kh*kw)."""

@@ -449,13 +449,15 @@ def test_mse_scales_match_oracle(cuda, R, C, g, dtype):
 # ------------------------------------------------------------------ compact launches
 @pytest.mark.parametrize("R,C,g,dtype,math", [(200, 512, 128, torch.bfloat16, MATH_TENSOR), (64, 384, 64, torch.float16, MATH_TENSOR),
                                               (333, 640, 32, torch.float32, MATH_TENSOR), (130, 512, 512, torch.bfloat16, MATH_FP32),
-                                              (96, 392, 56, torch.float16, MATH_TENSOR)])
+                                              (96, 392, 56, torch.float16, MATH_TENSOR), (2500, 256, 64, torch.bfloat16, MATH_TENSOR)])
 def test_compact_sweep_is_bit_identical(cuda, R, C, g, dtype, math):
     """MQ_MATH_COMPACT only changes the launch shape of the sweep's full tiles (one weight row per
     thread instead of eight lanes per row): codes, dequantized values, packed words and scales
     must be the same bits, through the whole-layer call and through the sweep alone with zero
     points and the factor of the inverse (the reference's form of the recurrence).  The last case
-    (group 56, C = 3 tiles + 8) has no tile the row kernel takes and a narrow last tile."""
+    (group 56, C = 3 tiles + 8) has no tile the row kernel takes and a narrow last tile.  2500 rows
+    are more than the grid of the sixteen-lane shape holds at once: such layers take eight lanes
+    per row, and that case is also held to the CPU oracle."""
     W = synthetic.layer_weight(R, C, 3, dtype).to(cuda)
     X = synthetic.activations(2 * C, C, 4, dtype).to(cuda)
     H = torch.zeros(C, C, device=cuda)
@@ -467,6 +469,10 @@ def test_compact_sweep_is_bit_identical(cuda, R, C, g, dtype, math):
     (c0, s0, d0, f0, p0), (c1, s1, d1, f1, p1) = outs
     assert torch.equal(c0[0], c1[0]) and torch.equal(s0[0], s1[0]) and torch.equal(p0[0], p1[0])
     assert torch.equal(d0[0].float(), d1[0].float()) and torch.equal(f0, f1)
+    if R > 2368:
+        want = O.quantize_layer(W.cpu(), H.cpu().clone(), bits=4, group_size=g, rel_damp=1e-2, block_size=128)
+        assert torch.equal(s0[0].cpu(), want["scale"].float())
+        assert O.code_agreement(c0[0].cpu(), want["qweight"]) >= CODE_AGREEMENT
 
     # the sweep alone: factor of the inverse, per-group zero points
     Hd = H.clone()

@@ -56,8 +56,8 @@ typedef enum { MQ_MATH_FP32 = 0, MQ_MATH_TENSOR = 1 } mq_math;
  * their *_workspace_bytes): the caller processes several layers at once on different streams
  * (gptq.quantize_many).  The library then prefers launch shapes that occupy few SMs over the
  * lowest latency of a single layer: the sweep's tiles run one weight row per thread on R/64
- * SMs instead of sixteen lanes per row on R/8 CTAs, and a CTA of a rank-128 strip update walks a whole
- * row of output tiles.  Results are bit-identical with and without it. */
+ * SMs instead of sixteen lanes per row on R/8 CTAs, a CTA of a rank-128 strip update walks a whole
+ * row of output tiles, a CTA of a panel solve takes 64 rows instead of 32.  Results are bit-identical with and without it. */
 #define MQ_MATH_COMPACT 0x100
 
 /* Device-side status of one layer, written by mq_hessian_prepare / mq_hinv_upper.

@@ -35,13 +35,13 @@ constexpr int SUPER_PANELS = 4;               // panels whose far update is appl
 constexpr int SUPER_NB = SUPER_PANELS * NB;   // 512
 
 // ------------------------------------------------------------------ diagonal block
-// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  256 threads; thread
-// (tr, tc) keeps the 8x8 tile at rows 8tr.., columns 8tc.. in registers, and the 16 tiles of a
-// tile column are the lanes of one half-warp.  The 128 pivots are taken 8 at a time (a "leaf",
-// tile column 15 first).  One warp's instruction stream runs at a fraction of an instruction
-// per cycle here (every step depends on the one before), so a leaf is arranged to put as few
-// instructions as possible in any one stream:
-//   1. the half-warp that holds tile column kt writes its tiles to shared memory, one row of
+// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  512 threads; the block is
+// cut into 8x8 tiles, warp tc holds tile column tc, and the tile at rows 8tr.. is split between
+// lanes tr (upper four rows) and 16 + tr (lower four), 32 registers each.  The 128 pivots are taken
+// 8 at a time (a "leaf", tile column 15 first).  One warp's instruction stream runs at a fraction
+// of an instruction per cycle here (every step depends on the one before), so a leaf is arranged
+// to put as few instructions as possible in any one stream:
+//   1. the warp that holds tile column kt writes its tiles to shared memory, one row of
 //      the block per shared-memory column;
 //   2. thread r of the first four warps takes ROW r of that column strip: it factors its own copy
 //      of the 8x8 leaf in registers (the same arithmetic in every thread, no communication
@@ -49,13 +49,15 @@ constexpr int SUPER_NB = SUPER_PANELS * NB;   // 512
 //      of one half-warp solving eight rows per lane; the rows of the leaf itself write the
 //      factored leaf back;
 //   3. the strip, now the panel of T above the leaf plus the leaf's factor, is read back by
-//      the half-warp that owns it, and every remaining upper tile takes one rank-8 update from it.
+//      the warp that owns it, and every remaining upper tile takes one rank-8 update from it.
 // The solved strip is double buffered so that the next leaf may be written while slower warps
 // still read this one.
 constexpr int PAN_LD = NB + 4;
 
-__global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
-                                                            int k_global, mq_layer_flags* flags) {
+constexpr int DIAG_THREADS = 512;
+
+__global__ void __launch_bounds__(DIAG_THREADS) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
+                                                                     int k_global, mq_layer_flags* flags) {
   // raw[kk][row]: column 8kt+kk of the strip as its owners hold it; pan[buf][kk][row]: the same
   // strip solved (the panel of T above the leaf, and the leaf's factor).  Two arrays, because a
   // thread may still be reading the raw leaf when another has its row ready.
@@ -65,27 +67,28 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
   chain_release();
   const int t = threadIdx.x;
   const int warp = t >> 5, lane = t & 31;
-  const int tc = warp * 2 + (lane >> 4), tr = lane & 15;
-  float a[8][8];
+  // warp = tile column; the two half-warps hold the upper and the lower four rows of its tiles
+  const int tc = warp, tr = lane & 15, r0 = tr * 8 + (lane >> 4) * 4;
+  float a[4][8];
   // Only tiles on or above the diagonal are ever read.  A whole, 16-byte aligned block moves
   // as float4 (a quarter of the memory transactions of scalar accesses at this tile layout).
   const bool vec = nb == NB && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(blk) & 15) == 0;
   if (vec) {
     if (tr <= tc) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 lo = *reinterpret_cast<const float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8);
-        const float4 hi = *reinterpret_cast<const float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8 + 4);
+      for (int i = 0; i < 4; ++i) {
+        const float4 lo = *reinterpret_cast<const float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8);
+        const float4 hi = *reinterpret_cast<const float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8 + 4);
         a[i][0] = lo.x; a[i][1] = lo.y; a[i][2] = lo.z; a[i][3] = lo.w;
         a[i][4] = hi.x; a[i][5] = hi.y; a[i][6] = hi.z; a[i][7] = hi.w;
       }
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        int r = tr * 8 + i, c = tc * 8 + j;
+        int r = r0 + i, c = tc * 8 + j;
         a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
       }
   }
@@ -94,10 +97,8 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
     // ---- 1. the strip of tile column kt goes to shared memory, transposed
     if (tc == kt && tr <= kt) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        *reinterpret_cast<float4*>(&raw[kk][tr * 8]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-        *reinterpret_cast<float4*>(&raw[kk][tr * 8 + 4]) = make_float4(a[4][kk], a[5][kk], a[6][kk], a[7][kk]);
-      }
+      for (int kk = 0; kk < 8; ++kk)
+        *reinterpret_cast<float4*>(&raw[kk][r0]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
     }
     __syncthreads();
     // ---- 2. one row of the strip per thread
@@ -162,24 +163,21 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
     if (tc == kt && tr <= kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const float4 lo = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8]);
-        const float4 hi = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8 + 4]);
-        a[0][kk] = lo.x; a[1][kk] = lo.y; a[2][kk] = lo.z; a[3][kk] = lo.w;
-        a[4][kk] = hi.x; a[5][kk] = hi.y; a[6][kk] = hi.z; a[7][kk] = hi.w;
+        const float4 v = *reinterpret_cast<const float4*>(&pan[buf][kk][r0]);
+        a[0][kk] = v.x; a[1][kk] = v.y; a[2][kk] = v.z; a[3][kk] = v.w;
       }
     }
     if (tr <= tc && tc < kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const float4 i0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8]);
-        const float4 i1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tr * 8 + 4]);
+        const float4 i0 = *reinterpret_cast<const float4*>(&pan[buf][kk][r0]);
         const float4 j0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8]);
         const float4 j1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8 + 4]);
-        const float pi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+        const float pi[4] = {i0.x, i0.y, i0.z, i0.w};
         const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
         // two columns per instruction (packed fp32 FMA: each half is an ordinary fma.rn)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
           const float2 npi = make_float2(-pi[i], -pi[i]);
 #pragma unroll
           for (int j = 0; j < 8; j += 2) {
@@ -193,21 +191,21 @@ __global__ void __launch_bounds__(256) chol_diag_rev_kernel(float* __restrict__ 
   }
   if (vec) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
       if (tr <= tc) {  // the diagonal tiles came back from the strip with zeros below their diagonal
         lo = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
         hi = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
       }
-      *reinterpret_cast<float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8) = lo;
-      *reinterpret_cast<float4*>(blk + (int64_t)(tr * 8 + i) * ld + tc * 8 + 4) = hi;
+      *reinterpret_cast<float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8) = lo;
+      *reinterpret_cast<float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8 + 4) = hi;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        int r = tr * 8 + i, c = tc * 8 + j;
+        int r = r0 + i, c = tc * 8 + j;
         if (r < nb && c < nb) blk[(int64_t)r * ld + c] = (r <= c) ? a[i][j] : 0.0f;
       }
   }
@@ -512,7 +510,7 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
       float* dblk = H + k1 * ldh + k1;
       {
         ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
-        MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(256), 0, st, dblk, ldh, nb, (int)k1, flags));
+        MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(DIAG_THREADS), 0, st, dblk, ldh, nb, (int)k1, flags));
       }
       MQ_LAUNCH_CHECK();
       if (k1 == 0) break;

@@ -35,86 +35,66 @@ constexpr int SUPER_PANELS = 4;               // panels whose far update is appl
 constexpr int SUPER_NB = SUPER_PANELS * NB;   // 512
 
 // ------------------------------------------------------------------ diagonal block
-// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T.  512 threads; the block is
-// cut into 8x8 tiles, warp tc holds tile column tc, and the tile at rows 8tr.. is split between
-// lanes tr (upper four rows) and 16 + tr (lower four), 32 registers each.  The 128 pivots are taken
-// 8 at a time (a "leaf", tile column 15 first).  One warp's instruction stream runs at a fraction
-// of an instruction per cycle here (every step depends on the one before), so a leaf is arranged
-// to put as few instructions as possible in any one stream:
-//   1. the warp that holds tile column kt writes its tiles to shared memory, one row of
-//      the block per shared-memory column;
-//   2. thread r of the first four warps takes ROW r of that column strip: it factors its own copy
-//      of the 8x8 leaf in registers (the same arithmetic in every thread, no communication
-//      inside the chain of 8 pivots) and solves its own row against it, 36 operations, instead
-//      of one half-warp solving eight rows per lane; the rows of the leaf itself write the
-//      factored leaf back;
-//   3. the strip, now the panel of T above the leaf plus the leaf's factor, is read back by
-//      the warp that owns it, and every remaining upper tile takes one rank-8 update from it.
-// The solved strip is double buffered so that the next leaf may be written while slower warps
-// still read this one.
+// D (nb x nb, upper triangle valid) -> T_d upper with D = T_d T_d^T, one CTA of 512 threads.
+// The block lives in shared memory.  The 128 pivots are taken 8 at a time (a "leaf", columns
+// 8kt..8kt+7, kt = 15 first).  One warp's instruction stream runs at a fraction of an instruction
+// per cycle here (every step depends on the one before), so a leaf is arranged to put as few
+// instructions as possible in any one stream:
+//   a. thread r < 8kt + 8 takes ROW r of the column strip: it factors its own copy of the 8x8
+//      leaf in registers (the same arithmetic in every thread, no communication inside the chain
+//      of 8 pivots) and solves its own row against it; the row's eight results are final: they go
+//      to global memory at once and, transposed, to the panel buffer;
+//   b. every element on or above the diagonal tiles in front of the strip takes its rank-8 update
+//      from the panel buffer.  The region shrinks with every leaf, so its 4x4 micro-tiles are dealt
+//      out to all 512 threads anew each time (with the tiles in registers of fixed owners, four
+//      fifths of the lanes idled through this phase, which the FMA pipe of the one SM bounds).
 constexpr int PAN_LD = NB + 4;
-
 constexpr int DIAG_THREADS = 512;
+constexpr int DIAG_LD = NB + 4;   // row stride of the block in shared memory (16-byte aligned rows)
+constexpr size_t kDiagSmem = (size_t)NB * DIAG_LD * sizeof(float);
 
 __global__ void __launch_bounds__(DIAG_THREADS) chol_diag_rev_kernel(float* __restrict__ blk, int64_t ld, int nb,
                                                                      int k_global, mq_layer_flags* flags) {
-  // raw[kk][row]: column 8kt+kk of the strip as its owners hold it; pan[buf][kk][row]: the same
-  // strip solved (the panel of T above the leaf, and the leaf's factor).  Two arrays, because a
-  // thread may still be reading the raw leaf when another has its row ready.
-  __shared__ __align__(16) float raw[8][PAN_LD];
-  __shared__ __align__(16) float pan[2][8][PAN_LD];
+  extern __shared__ __align__(16) float Ms[];         // [NB][DIAG_LD]: the block, tiles on and above the diagonal
+  __shared__ __align__(16) float pan[8][PAN_LD];      // pan[kk][row]: column 8kt+kk of the solved strip
   chain_wait();
   chain_release();
   const int t = threadIdx.x;
-  const int warp = t >> 5, lane = t & 31;
-  // warp = tile column; the two half-warps hold the upper and the lower four rows of its tiles
-  const int tc = warp, tr = lane & 15, r0 = tr * 8 + (lane >> 4) * 4;
-  float a[4][8];
-  // Only tiles on or above the diagonal are ever read.  A whole, 16-byte aligned block moves
-  // as float4 (a quarter of the memory transactions of scalar accesses at this tile layout).
+  // A whole, 16-byte aligned block moves as float4; rows and columns past nb read as the identity.
   const bool vec = nb == NB && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(blk) & 15) == 0;
-  if (vec) {
-    if (tr <= tc) {
+  for (int idx = t; idx < NB * NB / 4; idx += DIAG_THREADS) {
+    const int r = idx >> 5, c4 = (idx & 31) * 4;
+    if ((c4 >> 3) < (r >> 3)) continue;               // tiles below the diagonal are never read
+    float4 v;
+    if (vec) {
+      v = *reinterpret_cast<const float4*>(blk + (int64_t)r * ld + c4);
+    } else {
+      float e[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 lo = *reinterpret_cast<const float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8);
-        const float4 hi = *reinterpret_cast<const float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8 + 4);
-        a[i][0] = lo.x; a[i][1] = lo.y; a[i][2] = lo.z; a[i][3] = lo.w;
-        a[i][4] = hi.x; a[i][5] = hi.y; a[i][6] = hi.z; a[i][7] = hi.w;
-      }
+      for (int q = 0; q < 4; ++q) e[q] = (r < nb && c4 + q < nb) ? blk[(int64_t)r * ld + c4 + q] : (r == c4 + q ? 1.0f : 0.0f);
+      v = make_float4(e[0], e[1], e[2], e[3]);
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        int r = r0 + i, c = tc * 8 + j;
-        a[i][j] = (r < nb && c < nb) ? blk[(int64_t)r * ld + c] : (r == c ? 1.0f : 0.0f);
-      }
+    *reinterpret_cast<float4*>(&Ms[r * DIAG_LD + c4]) = v;
   }
+  __syncthreads();
   for (int kt = 15; kt >= 0; --kt) {
-    const int buf = kt & 1;
-    // ---- 1. the strip of tile column kt goes to shared memory, transposed
-    if (tc == kt && tr <= kt) {
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        *reinterpret_cast<float4*>(&raw[kk][r0]) = make_float4(a[0][kk], a[1][kk], a[2][kk], a[3][kk]);
-    }
-    __syncthreads();
-    // ---- 2. one row of the strip per thread
+    // ---- a. one row of the strip per thread
     const int row = t;
     if (row < kt * 8 + 8) {
       float L[8][8];   // L[i][j] = leaf element (row 8kt+i, column 8kt+j), upper triangle
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 lo = *reinterpret_cast<const float4*>(&raw[j][kt * 8]);
-        const float4 hi = *reinterpret_cast<const float4*>(&raw[j][kt * 8 + 4]);
-        L[0][j] = lo.x; L[1][j] = lo.y; L[2][j] = lo.z; L[3][j] = lo.w;
-        L[4][j] = hi.x; L[5][j] = hi.y; L[6][j] = hi.z; L[7][j] = hi.w;
+      for (int i = 0; i < 8; ++i) {
+        const float4 lo = *reinterpret_cast<const float4*>(&Ms[(kt * 8 + i) * DIAG_LD + kt * 8]);
+        const float4 hi = *reinterpret_cast<const float4*>(&Ms[(kt * 8 + i) * DIAG_LD + kt * 8 + 4]);
+        L[i][0] = lo.x; L[i][1] = lo.y; L[i][2] = lo.z; L[i][3] = lo.w;
+        L[i][4] = hi.x; L[i][5] = hi.y; L[i][6] = hi.z; L[i][7] = hi.w;
       }
       float x[8];
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) x[kk] = raw[kk][row];
+      {
+        const float4 lo = *reinterpret_cast<const float4*>(&Ms[row * DIAG_LD + kt * 8]);
+        const float4 hi = *reinterpret_cast<const float4*>(&Ms[row * DIAG_LD + kt * 8 + 4]);
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w; x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+      }
       // The 8 pivots are one straight line of code (no branch), so that the scheduler can put
       // the row arithmetic of pivot kk into the latency of pivot kk-1's rsqrt chain.  The rows
       // of the leaf itself run the row arithmetic too; that copy is discarded below.
@@ -156,58 +136,66 @@ __global__ void __launch_bounds__(DIAG_THREADS) chol_diag_rev_kernel(float* __re
         }
       }
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) pan[buf][kk][row] = x[kk];
+      for (int kk = 0; kk < 8; ++kk) pan[kk][row] = x[kk];
+      // the strip is final
+      if (vec) {
+        *reinterpret_cast<float4*>(blk + (int64_t)row * ld + kt * 8) = make_float4(x[0], x[1], x[2], x[3]);
+        *reinterpret_cast<float4*>(blk + (int64_t)row * ld + kt * 8 + 4) = make_float4(x[4], x[5], x[6], x[7]);
+      } else if (row < nb) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          if (kt * 8 + kk < nb) blk[(int64_t)row * ld + kt * 8 + kk] = x[kk];
+      }
+    } else if (row < NB) {
+      // below the leaf: zeros
+      if (vec) {
+        *reinterpret_cast<float4*>(blk + (int64_t)row * ld + kt * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(blk + (int64_t)row * ld + kt * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else if (row < nb) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          if (kt * 8 + kk < nb) blk[(int64_t)row * ld + kt * 8 + kk] = 0.0f;
+      }
     }
     __syncthreads();
-    // ---- 3. the owners take the strip back; everything in front of it takes its rank-8 update
-    if (tc == kt && tr <= kt) {
+    // ---- b. rank-8 update of what lies in front of the strip: rows and columns below 8kt, 4x4
+    // micro-tiles on and above the diagonal 8x8 tiles.  n micro-rows (even); rows i and n-1-i
+    // together hold n + 1 micro-tiles on or right of the diagonal, which makes the triangle a
+    // rectangle of n/2 x (n + 1) items.  (A micro-tile left of the diagonal micro-tile of its
+    // row but inside a diagonal 8x8 tile is never read: it is skipped with the rest.)
+    const int n = 2 * kt;
+    const int items = (n >> 1) * (n + 1);
+    for (int m = t; m < items; m += DIAG_THREADS) {
+      const int i = m / (n + 1), jj = m - i * (n + 1);
+      int mi, mj;
+      if (jj < n - i) { mi = i; mj = i + jj; }
+      else { mi = n - 1 - i; mj = mi + (jj - (n - i)); }
+      const int r0 = 4 * mi, c0 = 4 * mj;
+      float c[4][4];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const float4 v = *reinterpret_cast<const float4*>(&pan[buf][kk][r0]);
-        a[0][kk] = v.x; a[1][kk] = v.y; a[2][kk] = v.z; a[3][kk] = v.w;
+      for (int a = 0; a < 4; ++a) {
+        const float4 v = *reinterpret_cast<const float4*>(&Ms[(r0 + a) * DIAG_LD + c0]);
+        c[a][0] = v.x; c[a][1] = v.y; c[a][2] = v.z; c[a][3] = v.w;
       }
-    }
-    if (tr <= tc && tc < kt) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const float4 i0 = *reinterpret_cast<const float4*>(&pan[buf][kk][r0]);
-        const float4 j0 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8]);
-        const float4 j1 = *reinterpret_cast<const float4*>(&pan[buf][kk][tc * 8 + 4]);
-        const float pi[4] = {i0.x, i0.y, i0.z, i0.w};
-        const float pj[8] = {j0.x, j0.y, j0.z, j0.w, j1.x, j1.y, j1.z, j1.w};
+        const float4 pi4 = *reinterpret_cast<const float4*>(&pan[kk][r0]);
+        const float4 pj4 = *reinterpret_cast<const float4*>(&pan[kk][c0]);
+        const float pi[4] = {pi4.x, pi4.y, pi4.z, pi4.w};
         // two columns per instruction (packed fp32 FMA: each half is an ordinary fma.rn)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 npi = make_float2(-pi[i], -pi[i]);
-#pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            const float2 r2 = __ffma2_rn(npi, make_float2(pj[j], pj[j + 1]), make_float2(a[i][j], a[i][j + 1]));
-            a[i][j] = r2.x;
-            a[i][j + 1] = r2.y;
-          }
+        for (int a = 0; a < 4; ++a) {
+          const float2 npi = make_float2(-pi[a], -pi[a]);
+          const float2 q01 = __ffma2_rn(npi, make_float2(pj4.x, pj4.y), make_float2(c[a][0], c[a][1]));
+          const float2 q23 = __ffma2_rn(npi, make_float2(pj4.z, pj4.w), make_float2(c[a][2], c[a][3]));
+          c[a][0] = q01.x; c[a][1] = q01.y; c[a][2] = q23.x; c[a][3] = q23.y;
         }
       }
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+        *reinterpret_cast<float4*>(&Ms[(r0 + a) * DIAG_LD + c0]) = make_float4(c[a][0], c[a][1], c[a][2], c[a][3]);
     }
-  }
-  if (vec) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
-      if (tr <= tc) {  // the diagonal tiles came back from the strip with zeros below their diagonal
-        lo = make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
-        hi = make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
-      }
-      *reinterpret_cast<float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8) = lo;
-      *reinterpret_cast<float4*>(blk + (int64_t)(r0 + i) * ld + tc * 8 + 4) = hi;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        int r = r0 + i, c = tc * 8 + j;
-        if (r < nb && c < nb) blk[(int64_t)r * ld + c] = (r <= c) ? a[i][j] : 0.0f;
-      }
+    __syncthreads();
   }
 }
 
@@ -448,6 +436,7 @@ int configure_once() {
   int dev = 0;
   MQ_CUDA(cudaGetDevice(&dev));
   if (!done[dev & 63]) {
+    MQ_CUDA(cudaFuncSetAttribute(chol_diag_rev_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDiagSmem));
     MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
     MQ_CUDA(cudaFuncSetAttribute(trsm_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
     done[dev & 63] = true;
@@ -510,7 +499,7 @@ int chol_unit_factor(float* H, int64_t C, int64_t ldh, float* diag, int math, in
       float* dblk = H + k1 * ldh + k1;
       {
         ProfScope prof(PROF_CHOL_DIAG, (double)nb * nb * nb / 3.0, 0.0, st);
-        MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(DIAG_THREADS), 0, st, dblk, ldh, nb, (int)k1, flags));
+        MQ_CUDA(launch_chained(true, chol_diag_rev_kernel, dim3(1), dim3(DIAG_THREADS), kDiagSmem, st, dblk, ldh, nb, (int)k1, flags));
       }
       MQ_LAUNCH_CHECK();
       if (k1 == 0) break;

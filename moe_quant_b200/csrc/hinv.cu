@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(DIAG_THREADS) chol_diag_rev_kernel(float* __re
         const bool bad = !(d > 0.0f);  // also catches NaN
         fail = (bad && fail == 0) ? kk + 1 : fail;
         d = bad ? 1.0f : d;
-        float r = rsqrtf(d);
+        float r;                       // d is a positive, normal pivot (or 1): the hardware approximation, refined below
+        asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
         r = r * fmaf(-0.5f * d * r, r, 1.5f);  // one Newton step: r = 1/sqrt(d) to about 1 ulp
         L[kk][kk] = d * r;
 #pragma unroll

@@ -82,3 +82,36 @@ def test_expired_device_wait_is_reported_with_the_layer_flags(monkeypatch):
     monkeypatch.setattr(_lib, "engine_fault", lambda: 0)
     h._pending_flags = [torch.tensor([1, 0, 0, 5], dtype=torch.int32)]
     assert h.issue_nan_hessian and h.issue_non_invertible
+
+
+def test_tied_groups_and_compact_launch_scope():
+    """Host side of quantize_many: handles tied to one another form one group led by the owner of
+    the Hessian (wherever they stand in the list), a tied handle whose owner is not in the list
+    stands alone; inside `compact_launches` a handle asks for compact launch shapes and gets its
+    own precision object back afterwards, also when the body raises."""
+    from moe_quant_b200 import gptq, ops
+
+    def lin():
+        return nn.Linear(16, 8, bias=False)
+
+    gate0, gate1 = GPTQ(lin(), 8, True, 1e-2, 128), GPTQ(lin(), 8, True, 1e-2, 128)
+    up0 = GPTQ(lin(), 8, True, 1e-2, 128, tied_gptq_handle=gate0)
+    up1 = GPTQ(lin(), 8, True, 1e-2, 128, tied_gptq_handle=gate1)
+    down = GPTQ(lin(), 8, True, 1e-2, 128)
+    outsider = GPTQ(lin(), 8, True, 1e-2, 128, tied_gptq_handle=GPTQ(lin(), 8, True, 1e-2, 128))
+    handles = [up0, gate0, down, gate1, outsider, up1]
+    assert gptq._tied_groups(handles) == [[1, 0], [2], [3, 5], [4]]
+
+    assert down.precision is None
+    with gptq.compact_launches(down):
+        assert down.precision.compact and down.precision.sweep_math == ops.MATH_TENSOR | 0x100
+    assert down.precision is None
+    mine = ops.Precision(math=0)
+    down.precision = mine
+    with pytest.raises(RuntimeError):
+        with gptq.compact_launches(down):
+            assert down.precision.compact and down.precision.math == 0
+            raise RuntimeError("body failed")
+    assert down.precision is mine and not mine.compact
+    with gptq.compact_launches(down, on=False):
+        assert down.precision is mine
